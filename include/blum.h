@@ -256,8 +256,12 @@ int blum_rope_attn_decode_paged(blum_ctx* ctx, blum_kv* kv, int layer, const voi
  * until the process exits).  It never calls cudaMalloc, cudaFree or any allocating routine.
  *   - Limit: B * q_heads * max_splits * (head_dim + 2) * 4 bytes must fit in the buffer; larger requests are
  *     rejected with BLUM_ERR_INVALID and a message naming both sizes.
- *   - The first call on a device looks the buffer's device address up (one cudaGetSymbolAddress with that device
- *     current); make that first call before starting any stream capture.
+ *   - The first call on a device looks the buffer's device address up (one cudaGetSymbolAddress with that device made
+ *     current for the lookup and the caller's device restored afterwards); make that first call before starting any
+ *     stream capture.  Like every launch of this library, the call expects the context's device to be current.
+ *   - If sequences grew since the last call (blum_kv_seq_extend / seq_alloc / seq_free), the page table is uploaded
+ *     inside this call, which waits for the stream.  Call blum_kv_sync_tables() yourself after growing sequences
+ *     and before a capture or a latency-critical call; with a clean table this entry point only launches kernels.
  *   - All calls on a device share the one buffer.  Calls that may overlap on the GPU (different streams, or
  *     different contexts on the same device) race on it; calls ordered on one stream are safe, and nothing
  *     written by an earlier call is ever read by a later one. */

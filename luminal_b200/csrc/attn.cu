@@ -293,9 +293,16 @@ static float* g_attn_static_ptr[64] = {};
 static int attn_static_scratch(blum_ctx* ctx, float** out) {
     BLUM_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "static attention scratch: device index %d not supported", ctx->device);
     if (!g_attn_static_ptr[ctx->device]) {
-        BLUM_CUDA(ctx, cudaSetDevice(ctx->device));
+        // the lookup answers for the CURRENT device: make the context's device current for it and put the caller's back
+        int prev = -1;
+        BLUM_CUDA(ctx, cudaGetDevice(&prev));
+        if (prev != ctx->device) BLUM_CUDA(ctx, cudaSetDevice(ctx->device));
         float* ptr = nullptr;
-        BLUM_CUDA(ctx, cudaGetSymbolAddress((void**)&ptr, g_attn_static_scratch));
+        const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_attn_static_scratch);
+        if (prev != ctx->device) cudaSetDevice(prev);
+        if (e != cudaSuccess || !ptr)
+            return blum_fail(ctx, BLUM_ERR_CUDA, "static attention scratch: cudaGetSymbolAddress failed on device %d: %s", ctx->device,
+                             cudaGetErrorString(e));
         g_attn_static_ptr[ctx->device] = ptr;
     }
     *out = g_attn_static_ptr[ctx->device];

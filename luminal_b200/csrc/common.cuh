@@ -28,6 +28,7 @@ struct blum_ctx {
     int trace_cap = 0, trace_next = 0;
     void* gemm_ws = nullptr;           // f32 workspace of the split-K tensor-core GEMM (grown on demand)
     size_t gemm_ws_bytes = 0;
+    std::vector<void*> retired;        // outgrown workspaces: captured graphs may still name them, freed with the context
 };
 
 // next trace record of this context (null when tracing is off or the buffer is full)

@@ -50,6 +50,7 @@ int blum_ctx_destroy(blum_ctx* ctx) {
     }
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     if (ctx->gemm_ws) cudaFree(ctx->gemm_ws);
+    for (void* r : ctx->retired) cudaFree(r);
     if (ctx->trace) cudaFree(ctx->trace);
     if (ctx->dev_error) cudaFree(ctx->dev_error);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);

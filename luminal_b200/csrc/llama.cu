@@ -210,7 +210,7 @@ static int pick_nsplit(const blum_ctx* ctx, const blum_llama* m, int R, int64_t 
     return n < 1 ? 1 : n;
 }
 
-static int run_decode_graph(blum_ctx* ctx, blum_llama* m, int R, int nsplit) {
+static int run_decode_step(blum_ctx* ctx, blum_llama* m, int R, int nsplit) {
     auto key = std::make_pair(R, nsplit);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
@@ -369,7 +369,7 @@ int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out
     m->max_splits = 32;
     ALLOC(m->attn_scratch, blum_attn_decode_scratch_bytes(c.max_seqs, m->nq, d, m->max_splits) + 16);
     if (cudaHostAlloc((void**)&m->h_rows, (size_t)4 * R * 4, cudaHostAllocDefault) != cudaSuccess ||
-        cudaHostAlloc((void**)&m->h_next, (size_t)c.max_seqs * 4, cudaHostAllocDefault) != cudaSuccess) {
+        cudaHostAlloc((void**)&m->h_next, (size_t)(c.max_seqs + 1) * 4, cudaHostAllocDefault) != cudaSuccess) {
         blum_fail(ctx, BLUM_ERR_OOM, "llama_create: pinned allocation failed");
         return fail(BLUM_ERR_OOM);
     }
@@ -496,29 +496,57 @@ int blum_llama_prefill(blum_ctx* ctx, blum_llama* m, int seq, const int32_t* hos
     return blum_check_device_error(ctx);
 }
 
+// Reads the device error word in the same synchronisation as the step's result: h_next[max_seqs] mirrors it.
+static int finish_step(blum_ctx* ctx, blum_llama* m, const char* what) {
+    int32_t* h_err = m->h_next + m->cfg.max_seqs;
+    BLUM_CUDA(ctx, cudaMemcpyAsync(h_err, ctx->dev_error, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*h_err != 0) {
+        const int word = *h_err;
+        BLUM_CUDA(ctx, cudaMemsetAsync(ctx->dev_error, 0, sizeof(int), ctx->stream));
+        return blum_fail(ctx, BLUM_ERR_DEVICE, "%s: device error word = 0x%x (bounded wait expired or bad page / sequence index)", what, word);
+    }
+    return BLUM_OK;
+}
+
 int blum_llama_decode(blum_ctx* ctx, blum_llama* m, const int32_t* seq_ids, const int32_t* host_ids, int64_t B,
                       int32_t* next_tokens, float* logits_out) {
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, m && seq_ids && host_ids && next_tokens, "llama_decode: null argument");
     BLUM_REQUIRE(ctx, B > 0 && B <= m->cfg.max_seqs, "llama_decode: batch %lld outside [1,%d]", (long long)B, m->cfg.max_seqs);
-    int64_t max_len = 0;
+    // validate every row before any sequence grows, so that a rejected call leaves the cache as it was
     for (int b = 0; b < B; b++) {
-        const int64_t len = blum_kv_seq_len(m->kv, seq_ids[b]);
-        if (len < 0) return blum_fail(ctx, BLUM_ERR_STATE, "llama_decode: sequence %d is not allocated", seq_ids[b]);
+        if (blum_kv_seq_len(m->kv, seq_ids[b]) < 0) return blum_fail(ctx, BLUM_ERR_STATE, "llama_decode: sequence %d is not allocated", seq_ids[b]);
         BLUM_REQUIRE(ctx, host_ids[b] >= 0 && host_ids[b] < m->cfg.vocab, "llama_decode: token id %d out of range", host_ids[b]);
-        TRY(blum_kv_seq_extend(ctx, m->kv, seq_ids[b], len + 1));
+        for (int a = 0; a < b; a++) BLUM_REQUIRE(ctx, seq_ids[a] != seq_ids[b], "llama_decode: sequence %d appears twice in the batch", seq_ids[b]);
+    }
+    std::vector<int64_t> old_len((size_t)B);
+    int64_t max_len = 0;
+    int grown = 0, rc = BLUM_OK;
+    for (int b = 0; b < B && !rc; b++) {
+        const int64_t len = blum_kv_seq_len(m->kv, seq_ids[b]);
+        old_len[b] = len;
+        rc = blum_kv_seq_extend(ctx, m->kv, seq_ids[b], len + 1);
+        if (rc) break;
+        grown = b + 1;
         m->h_rows[b] = host_ids[b];
         m->h_rows[m->max_rows + b] = seq_ids[b];
         m->h_rows[2 * m->max_rows + b] = (int32_t)len;
         m->h_rows[3 * m->max_rows + b] = (int32_t)len + 1;
         if (len + 1 > max_len) max_len = len + 1;
     }
-    TRY(blum_kv_sync_tables(ctx, m->kv));
-    TRY(upload_rows(ctx, m, (int)B));
-    TRY(run_decode_graph(ctx, m, (int)B, pick_nsplit(ctx, m, (int)B, max_len)));
-    BLUM_CUDA(ctx, cudaMemcpyAsync(m->h_next, m->d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (logits_out) BLUM_CUDA(ctx, cudaMemcpyAsync(logits_out, m->logits, (size_t)B * m->vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // a failed step must not leave sequences one token longer than what the cache holds (pages stay with the sequence)
+    auto roll_back = [&]() { for (int b = 0; b < grown; b++) m->kv->seq_len[seq_ids[b]] = old_len[b]; };
+    if (!rc) rc = blum_kv_sync_tables(ctx, m->kv);
+    if (!rc) rc = upload_rows(ctx, m, (int)B);
+    if (!rc) rc = run_decode_step(ctx, m, (int)B, pick_nsplit(ctx, m, (int)B, max_len));
+    if (!rc) {
+        cudaError_t e = cudaMemcpyAsync(m->h_next, m->d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess && logits_out) e = cudaMemcpyAsync(logits_out, m->logits, (size_t)B * m->vocab * 4, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e != cudaSuccess) rc = blum_fail(ctx, BLUM_ERR_CUDA, "llama_decode: result copy failed: %s", cudaGetErrorString(e));
+    }
+    if (!rc) rc = finish_step(ctx, m, "llama_decode");
+    if (rc) { roll_back(); return rc; }
     memcpy(next_tokens, m->h_next, (size_t)B * 4);
     return BLUM_OK;
 }
@@ -529,30 +557,32 @@ int blum_llama_decode_loop(blum_ctx* ctx, blum_llama* m, int seq, int32_t first_
     const int64_t len = blum_kv_seq_len(m->kv, seq);
     if (len < 0) return blum_fail(ctx, BLUM_ERR_STATE, "llama_decode_loop: sequence %d is not allocated", seq);
     BLUM_REQUIRE(ctx, first_token >= 0 && first_token < m->cfg.vocab, "llama_decode_loop: token id out of range");
-    TRY(blum_kv_seq_extend(ctx, m->kv, seq, len + steps));
-    TRY(blum_kv_sync_tables(ctx, m->kv));
-    if (m->hist_cap < steps) {
+    if (m->hist_cap < steps) {     // grown before the sequence is, so that a failed allocation changes nothing
         if (m->d_hist) cudaFree(m->d_hist);
-        m->d_hist = nullptr;
+        m->d_hist = nullptr; m->hist_cap = 0;
         BLUM_CUDA(ctx, cudaMalloc((void**)&m->d_hist, (size_t)steps * 4));
         m->hist_cap = steps;
     }
-    m->h_rows[0] = first_token;
-    m->h_rows[m->max_rows] = seq;
-    m->h_rows[2 * m->max_rows] = (int32_t)len;
-    m->h_rows[3 * m->max_rows] = (int32_t)len + 1;
-    TRY(upload_rows(ctx, m, 1));
-    const int nsplit = pick_nsplit(ctx, m, 1, len + steps);
-    for (int s = 0; s < steps; s++) {
-        TRY(run_decode_graph(ctx, m, 1, nsplit));
-        advance_rows_kernel<<<1, 32, 0, ctx->stream>>>(m->d_rows, m->max_rows, m->d_next, m->d_hist, s, 1);
-        BLUM_LAUNCH_CHECK(ctx);
-    }
-    if (tokens_out) {
-        BLUM_CUDA(ctx, cudaMemcpyAsync(tokens_out, m->d_hist, (size_t)steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
-        BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    }
-    return BLUM_OK;
+    TRY(blum_kv_seq_extend(ctx, m->kv, seq, len + steps));
+    auto body = [&]() -> int {
+        TRY(blum_kv_sync_tables(ctx, m->kv));
+        m->h_rows[0] = first_token;
+        m->h_rows[m->max_rows] = seq;
+        m->h_rows[2 * m->max_rows] = (int32_t)len;
+        m->h_rows[3 * m->max_rows] = (int32_t)len + 1;
+        TRY(upload_rows(ctx, m, 1));
+        const int nsplit = pick_nsplit(ctx, m, 1, len + steps);
+        for (int s = 0; s < steps; s++) {
+            TRY(run_decode_step(ctx, m, 1, nsplit));
+            advance_rows_kernel<<<1, 32, 0, ctx->stream>>>(m->d_rows, m->max_rows, m->d_next, m->d_hist, s, 1);
+            BLUM_LAUNCH_CHECK(ctx);
+        }
+        if (tokens_out) BLUM_CUDA(ctx, cudaMemcpyAsync(tokens_out, m->d_hist, (size_t)steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        return finish_step(ctx, m, "llama_decode_loop");
+    };
+    const int rc = body();
+    if (rc) m->kv->seq_len[seq] = len;
+    return rc;
 }
 
 }  // extern "C"

@@ -446,12 +446,8 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
         if (ydt == BLUM_F32) ws = (float*)y;
         else {
             const size_t need = (size_t)M * N * sizeof(float);
-            if (ctx->gemm_ws_bytes < need) {
-                if (ctx->gemm_ws) BLUM_CUDA(ctx, cudaFree(ctx->gemm_ws));
-                ctx->gemm_ws = nullptr; ctx->gemm_ws_bytes = 0;
-                BLUM_CUDA(ctx, cudaMalloc(&ctx->gemm_ws, need));
-                ctx->gemm_ws_bytes = need;
-            }
+            const int wrc = blum_gemm_ws_reserve(ctx, need);
+            if (wrc) return wrc;
             ws = (float*)ctx->gemm_ws;
         }
         BLUM_CUDA(ctx, cudaMemsetAsync(ws, 0, (size_t)M * N * sizeof(float), ctx->stream));
@@ -471,11 +467,20 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
 }
 
 // Grows the split-K workspace ahead of time (model objects call this at creation so that captured steps never allocate).
+// A workspace that was ever handed to a kernel is never freed while the context lives: captured CUDA graphs (a model's
+// decode step, anything recorded between blum_graph_begin/end) keep its address.  An outgrown buffer moves to the context's
+// retired list and is released by blum_ctx_destroy.  Growth is refused while the stream is capturing, because cudaMalloc
+// would invalidate the capture.
 int blum_gemm_ws_reserve(blum_ctx* ctx, size_t bytes) {
     if (ctx->gemm_ws_bytes >= bytes) return BLUM_OK;
-    if (ctx->gemm_ws) BLUM_CUDA(ctx, cudaFree(ctx->gemm_ws));
-    ctx->gemm_ws = nullptr; ctx->gemm_ws_bytes = 0;
-    BLUM_CUDA(ctx, cudaMalloc(&ctx->gemm_ws, bytes));
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone)
+        return blum_fail(ctx, BLUM_ERR_STATE, "matmul workspace of %zu bytes requested during stream capture (have %zu): run the "
+                         "largest shape once, or create the model, before capturing", bytes, ctx->gemm_ws_bytes);
+    void* fresh = nullptr;
+    BLUM_CUDA(ctx, cudaMalloc(&fresh, bytes));
+    if (ctx->gemm_ws) ctx->retired.push_back(ctx->gemm_ws);
+    ctx->gemm_ws = fresh;
     ctx->gemm_ws_bytes = bytes;
     return BLUM_OK;
 }

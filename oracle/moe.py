@@ -81,20 +81,31 @@ def permute(ids, E):
 
 
 def swish(g):
-    return g * (1.0 / (1.0 + np.exp(-g)))
+    # g / (1 + exp(-g)); the exponent is capped so that very negative g gives g * tiny instead of an overflow warning
+    g = np.asarray(g, np.float32)
+    return g * (np.float32(1.0) / (np.float32(1.0) + np.exp(np.minimum(-g, np.float32(88.0)))))
+
+
+def moe_ffn_lazy(x, router_w, router_bias, expert, k):
+    """x [T,H] (bf16 values); expert(e) -> (wg [I,H], wu [I,H], wd [H,I]) as f32, called once per expert that is hit
+    (full-size layers hold gigabytes of dequantised weights otherwise).  Returns (out f32 [T,H], ids, gates)."""
+    T = x.shape[0]
+    ids, gates, _ = route(x, router_w, router_bias, k)
+    out = np.zeros((T, x.shape[1]), np.float32)
+    contrib = np.zeros((T, k, x.shape[1]), np.float32)
+    for e in np.unique(ids):
+        wg, wu, wd = expert(int(e))
+        for t, j in zip(*np.nonzero(ids == e)):
+            g = round_bf16(wg @ x[t])
+            u = round_bf16(wu @ x[t])
+            mid = round_bf16(u * swish(g))
+            contrib[t, j] = round_bf16(wd @ mid)
+    for t in range(T):                       # the combine adds the k choices in choice order, in f32
+        for j in range(k):
+            out[t] += gates[t, j] * contrib[t, j]
+    return out, ids, gates
 
 
 def moe_ffn(x, router_w, router_bias, wg, wu, wd, k):
     """x [T,H] (bf16 values); wg/wu f32 [E,I,H]; wd f32 [E,H,I] (already dequantised).  Returns (out f32 [T,H], ids, gates)."""
-    T = x.shape[0]
-    ids, gates, _ = route(x, router_w, router_bias, k)
-    out = np.zeros((T, x.shape[1]), np.float32)
-    for t in range(T):
-        for j in range(k):
-            e = ids[t, j]
-            g = round_bf16(wg[e] @ x[t])
-            u = round_bf16(wu[e] @ x[t])
-            mid = round_bf16(u * swish(g))
-            y = round_bf16(wd[e] @ mid)
-            out[t] += gates[t, j] * y
-    return out, ids, gates
+    return moe_ffn_lazy(x, router_w, router_bias, lambda e: (wg[e], wu[e], wd[e]), k)

@@ -4,7 +4,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import TINY_CFG, assert_parity, make_weights
+from helpers import LLAMA8B_CFG, TINY_CFG, assert_parity, make_weights
 from luminal_b200 import BF16, F32, BlumError, runtime
 from luminal_b200.llama import Llama
 
@@ -114,6 +114,103 @@ def test_llama3_8b_layer_shapes(ctx, orc):
         assert int(out[0]) == orc.argmax(want)
         tok = int(out[0])
     m.destroy()
+
+
+def test_llama3_8b_full_model_32_greedy_ids(ctx, orc):
+    """The configuration the benchmark times, at its own size: 32 layers, vocabulary 128 256, seed 0, f32 activations and
+    KV.  A 32-token prompt and 32 greedy steps on the GPU and through the CPU oracle (weights kept quantised, all host
+    cores): the 32 token ids must be identical (examples/llama/src/main.rs:152-181, sampler :194-198) and the logits of every
+    step within the contract tolerance.  The top-2 logit gap of every step is printed for both sides, so that a mismatch can
+    be told apart from a near-tie."""
+    cfg = LLAMA8B_CFG
+    m = Llama(ctx, cfg, act_dtype=F32, page_size=16, max_seqs=1, max_ctx=80)
+    m.generate_weights(0)
+    w = make_weights(orc, cfg, seed=0)
+    ref = orc.Llama(cfg, w, ctx_cap=80)
+    prompt = orc.gen_token_ids(0, 1, 32, cfg["vocab"])
+    seq = m.new_sequence()
+    tok, logits = m.prefill(seq, prompt, want_logits=True)
+    want = ref.forward(prompt)
+    got_ids, want_ids, report = [], [], []
+    for step in range(32):
+        wtok = orc.argmax(want)
+        g2, w2 = np.partition(logits, -2)[-2:], np.partition(want, -2)[-2:]
+        report.append("step %2d: gpu id %6d gap %.3e | oracle id %6d gap %.3e | max |dlogit| %.2e" % (
+            step, tok, g2[1] - g2[0], wtok, w2[1] - w2[0], np.abs(logits - want).max()))
+        got_ids.append(int(tok))
+        want_ids.append(int(wtok))
+        assert_parity(logits, want, max_abs=1e-2, rel=2e-2, what="full-size logits, step %d\n%s" % (step, "\n".join(report)))
+        if tok != wtok or step == 31:
+            break
+        out, lg = m.decode([seq], [tok], want_logits=True)
+        tok, logits = int(out[0]), lg[0]
+        want = ref.forward([wtok])
+    print("\n".join(report))
+    assert got_ids == want_ids and len(got_ids) == 32, "\n".join(report)
+    ctx.check_device_error()
+    m.destroy()
+
+
+def test_decode_reports_a_device_error_and_leaves_the_sequence_as_it_was(ctx, orc, tiny):
+    """A page id outside the pool is caught by the kernels' index check (they skip the access and set the error word, no
+    fault): the decode call must come back with ERR_DEVICE instead of a garbage token, the sequence must not have grown,
+    and the same step must succeed once the table is repaired."""
+    from luminal_b200 import _lib
+    m, _ = tiny
+    prompt = orc.gen_token_ids(0, 3, 5, TINY_CFG["vocab"])
+    want = m.greedy(prompt, 3)
+    seq = m.new_sequence()
+    tok = m.prefill(seq, prompt)
+    assert tok == want[0]
+    n_before = m.kv.seq_len(seq)
+    table = m.kv.page_table()                                # synchronised copy of the device table
+    entry = int(seq) * m.kv.max_pages_per_seq + 1            # page of positions 4..7: the slot the next token is appended to
+    good = np.array([table.reshape(-1)[entry]], np.int32)
+    bad = np.array([m.kv.num_pages + 7], np.int32)
+    tbl = ctx.lib.blum_kv_page_table_dev(m.kv.h)
+    ctx._check(ctx.lib.blum_memcpy_h2d(ctx.h, tbl + 4 * entry, bad.ctypes.data, 4))
+    ctx.sync()
+    with pytest.raises(BlumError) as ei:
+        m.decode([seq], [tok])
+    assert ei.value.code == _lib.ERR_DEVICE
+    assert m.kv.seq_len(seq) == n_before
+    ctx._check(ctx.lib.blum_memcpy_h2d(ctx.h, tbl + 4 * entry, good.ctypes.data, 4))
+    ctx.sync()
+    ctx.check_device_error()                                 # the failed call already cleared the word
+    m.kv.seq_free(seq)
+    assert m.greedy(prompt, 3) == want
+
+
+def test_a_second_larger_model_leaves_the_first_models_captured_step_valid(ctx, orc):
+    """Model A (bf16, 5-row batches: tensor-core / small-batch GEMMs with an f32 workspace) decodes, then a larger model B is
+    created on the same context and runs, which outgrows the shared workspace.  A's captured step still names the old
+    buffer, which therefore must not have been freed: A decodes again and reproduces its own earlier tokens."""
+    w = make_weights(orc, TINY_CFG, seed=0)
+    a = Llama(ctx, TINY_CFG, act_dtype=BF16, page_size=16, max_seqs=5, max_ctx=64)
+    a.load_weights(w)
+    prompts = [orc.gen_token_ids(0, 40 + i, 4 + i, TINY_CFG["vocab"]) for i in range(5)]
+
+    def run(model):
+        seqs = [model.new_sequence() for _ in prompts]
+        toks = [[model.prefill(s, p)] for s, p in zip(seqs, prompts)]
+        for _ in range(4):
+            out = model.decode(seqs, [t[-1] for t in toks])
+            for t, o in zip(toks, out):
+                t.append(int(o))
+        for s in seqs:
+            model.kv.seq_free(s)
+        return toks
+
+    first = run(a)
+    big = dict(TINY_CFG, hidden=512, ffn=2048, q_heads=8, kv_heads=2, head_dim=64)
+    b = Llama(ctx, big, act_dtype=BF16, page_size=16, max_seqs=8, max_ctx=2048)
+    b.generate_weights(1)
+    sb = b.new_sequence()
+    b.prefill(sb, orc.gen_token_ids(0, 50, 300, big["vocab"]))
+    assert run(a) == first
+    ctx.check_device_error()
+    b.destroy()
+    a.destroy()
 
 
 def test_model_error_paths(ctx, tiny):

@@ -61,6 +61,38 @@ def test_moe_ffn_against_oracle(ctx, T):
         w.free()
 
 
+@pytest.mark.parametrize("T", [1, 64])
+def test_moe_ffn_at_the_full_layer_size(ctx, T):
+    """The MoE configuration's own dimensions (hidden = expert intermediate = 2880, 32 experts, top-4, Zipf-skewed router
+    bias): routing and permutation exact, values at the contract tolerance.  The oracle dequantises only the experts that
+    are hit, from the bytes the device holds; the device generator is checked against the oracle's on expert 0."""
+    H, I, E, k = 2880, 2880, 32, 4
+    ws = [Mxfp4Weight.generate(ctx, 4, 940 + i, E, n, kk) for i, (n, kk) in enumerate(((I, H), (I, H), (H, I)))]
+    host = [w.download() for w in ws]
+    q0, s0 = omoe.gen_mxfp4(4, 940, 1, I, H)       # the stream is indexed expert-major: expert 0 is its first N*K elements
+    assert np.array_equal(host[0][0][0], q0[0]) and np.array_equal(host[0][1][0], s0[0])
+    router = round_to_dtype(gen_normal(4, 950, E * H, 0.02).reshape(E, H), BF16)
+    bias = (-1.1 * np.log(np.arange(1, E + 1))).astype(np.float32)              # expert load roughly Zipf(1.1)
+    x = round_to_dtype(gen_normal(4, 951, T * H).reshape(T, H), BF16)
+    layer = MoeFfn(ctx, H, I, E, k, ctx.to_device(router, BF16), ctx.to_device(bias), *ws)
+    keep = {}
+    out = ctx.to_host(layer.forward(ctx.to_device(x, BF16), T, out_dtype=F32, keep=keep), F32, T * H).reshape(T, H)
+    ctx.check_device_error()
+    expert = lambda e: tuple(omoe.dequant_mxfp4(q[e], s[e]) for q, s in host)
+    want, ids, gates = omoe.moe_ffn_lazy(x, router, bias, expert, k)
+    assert np.array_equal(keep["ids"].download(np.int32, T * k).reshape(T, k), ids)
+    assert np.abs(ctx.to_host(keep["gates"], F32, T * k).reshape(T, k) - gates).max() < 1e-5
+    ss, so, off = omoe.permute(ids, E)
+    assert np.array_equal(keep["sorted_src"].download(np.int32, T * k), ss)
+    assert np.array_equal(keep["slot_of"].download(np.int32, T * k), so)
+    assert np.array_equal(keep["offsets"].download(np.int32, E + 1), off)
+    scale = np.abs(want).max()
+    assert_parity(out, want, max_abs=max(1e-2, 2e-2 * scale), rel=2e-2, what="moe ffn 2880/32/top-4 T=%d" % T)
+    assert np.abs(out - want).mean() < 4e-3 * scale
+    for w in ws:
+        w.free()
+
+
 def test_topk_ties_go_to_the_lower_expert(ctx):
     H, E, k, T = 64, 8, 4, 3
     router = np.zeros((E, H), np.float32)

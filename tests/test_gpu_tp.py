@@ -21,6 +21,45 @@ def _gpu_count():
         return 0
 
 
+def _run_ranks(target, size, per_item_timeout=240):
+    """Starts one daemon child per rank, collects one result tuple each (last field = traceback or None) and ALWAYS
+    terminates and joins every child, whatever happened: a rank that failed after the communicator was set up leaves
+    its peer inside a collective that cannot complete, so the parent ends the peers as soon as the first failure
+    is reported or a result does not arrive in time."""
+    ctxm = mp.get_context("spawn")
+    q = ctxm.Queue()
+    results = []
+    with tempfile.TemporaryDirectory() as td:
+        procs = [ctxm.Process(target=target, args=(r, size, os.path.join(td, "nccl_id"), q), daemon=True) for r in range(size)]
+        try:
+            for p in procs:
+                p.start()
+            for _ in range(size):
+                try:
+                    item = q.get(timeout=per_item_timeout)
+                except Exception:
+                    results.append((None, "no result from a rank within %d s" % per_item_timeout))
+                    break
+                results.append(item)
+                if item[-1] is not None:      # a rank failed: do not wait for its peers
+                    break
+        finally:
+            failed = any(r[-1] is not None for r in results) or len(results) < size
+            for p in procs:
+                if not failed:
+                    p.join(timeout=60)
+                if p.is_alive():
+                    p.terminate()             # this exact child only
+                    p.join(timeout=10)
+                if p.is_alive():
+                    p.kill()
+                    p.join(timeout=10)
+    for r in results:
+        assert r[-1] is None, "rank %s failed:\n%s" % (r[0], r[-1])
+    assert len(results) == size
+    return results
+
+
 def _rank_main(rank, size, id_path, out_q):
     try:
         here = os.path.dirname(os.path.abspath(__file__))
@@ -57,17 +96,7 @@ def _rank_main(rank, size, id_path, out_q):
 def test_tensor_parallel_greedy_ids_match_golden():
     size = 2
     g = np.load(os.path.join(GOLD, "oracle_vectors.npz"))
-    ctxm = mp.get_context("spawn")
-    q = ctxm.Queue()
-    with tempfile.TemporaryDirectory() as td:
-        procs = [ctxm.Process(target=_rank_main, args=(r, size, os.path.join(td, "nccl_id"), q)) for r in range(size)]
-        for p in procs:
-            p.start()
-        results = [q.get(timeout=240) for _ in range(size)]
-        for p in procs:
-            p.join(timeout=60)
-            if p.is_alive():
-                p.terminate()      # this exact child only
+    results = _run_ranks(_rank_main, size)
     for rank, ar, toks, err in results:
         assert err is None, "rank %d failed:\n%s" % (rank, err)
         assert ar == [3.0, 3.0, 3.0]                       # 1 + 2 summed over the two ranks
@@ -113,18 +142,7 @@ def _ep_rank_main(rank, size, id_path, out_q):
 def test_expert_parallel_moe_equals_the_single_gpu_layer():
     """Experts sharded over 2 ranks, tokens owned by their rank, rows exchanged with the NCCL all-to-all: every token's
     output is bit-identical to the unsharded layer run on the same GPU (each row's product does not depend on its neighbours)."""
-    size = 2
-    ctxm = mp.get_context("spawn")
-    q = ctxm.Queue()
-    with tempfile.TemporaryDirectory() as td:
-        procs = [ctxm.Process(target=_ep_rank_main, args=(r, size, os.path.join(td, "nccl_id"), q)) for r in range(size)]
-        for p in procs:
-            p.start()
-        results = [q.get(timeout=240) for _ in range(size)]
-        for p in procs:
-            p.join(timeout=60)
-            if p.is_alive():
-                p.terminate()      # this exact child only
+    results = _run_ranks(_ep_rank_main, 2)
     for rank, same, same2, peak, err in results:
         assert err is None, "rank %d failed:\n%s" % (rank, err)
         assert same and same2 and peak > 0, (rank, same, same2, peak)
