@@ -357,6 +357,13 @@ int blum_llama_decode(blum_ctx* ctx, blum_llama* m, const int32_t* seq_ids, cons
  * device, tokens_out host int32 [steps].  Used for device-only throughput timing. */
 int blum_llama_decode_loop(blum_ctx* ctx, blum_llama* m, int seq, int32_t first_token, int steps,
                            int32_t* tokens_out);
+/* How a single-sequence decode step is executed.  The reference has one way (Graph::execute interprets the node list,
+ * src/graph.rs:191-224); here there are two: path 0 (default) runs the step as one persistent kernel with a continuous
+ * weight stream when the model allows it (f32 activations and cache, head_dim 128, no tensor parallelism, hidden / ffn /
+ * q width multiples of 512) and falls back to path 1 otherwise; path 1 always replays the captured graph of per-op
+ * kernels.  blum_llama_decode_path returns the path a single-sequence step takes now: 2 = persistent kernel, 1 = graph. */
+int blum_llama_set_decode_path(blum_ctx* ctx, blum_llama* m, int path);
+int blum_llama_decode_path(blum_ctx* ctx, blum_llama* m);
 /* Borrowed handles to the model's own tensors, for per-kernel timing: which = 0 fused q/k/v, 1 attn_output,
  * 2 ffn_gate, 3 ffn_up, 4 ffn_down, 5 output head (layer ignored).  Norm weights: 0 attn_norm, 1 ffn_norm, 2 output_norm. */
 blum_q8_weight* blum_llama_layer_weight(blum_llama* m, int layer, int which);

@@ -4,14 +4,17 @@
 // The reference builds this model as a graph of ~10^3 primitive nodes per token
 // (examples/llama/src/model.rs:171-248 in luminal) and interprets it node by node with one allocation
 // and one launch each (src/graph.rs:191-224); the decode loop copies 128 256 logits to the host and
-// takes the argmax there (examples/llama/src/main.rs:152-181,194-198).  Here a decode step is
-// 6 launches per layer, captured once in a CUDA graph and replayed:
-//   [RMSNorm + fused q/k/v GEMV] [RoPE + KV append] [paged GQA attention]
+// takes the argmax there (examples/llama/src/main.rs:152-181,194-198).  Here a single-sequence decode step
+// (f32 activations and cache, head_dim 128, dimensions in multiples of 512) is ONE persistent kernel with a
+// continuous weight stream (decode_stream.cu) followed by the on-device argmax.  Other small batches
+// (up to GEMV_ROWS rows) are 5 launches per layer, captured once in a CUDA graph and replayed:
+//   [RMSNorm + fused q/k/v GEMV] [RoPE + KV append + paged GQA attention]
 //   [o_proj GEMV + residual] [RMSNorm + gate/up GEMV + SwiGLU] [down GEMV + residual]
-// plus the embedding gather, the [final norm + LM head GEMV] and an on-device argmax; only token ids
-// cross PCIe.  Steps with more than GEMV_ROWS rows (prefill, large batches) run the unfused sequence
-// norm -> matmul -> elementwise through the same entry points a luminal operator would call.
+// plus the embedding gather, the [final norm + LM head GEMV] and the argmax; only token ids cross PCIe.
+// Steps with more rows (prefill, large batches) run the unfused sequence norm -> matmul -> elementwise
+// through the same entry points a luminal operator would call.
 #include "kv.cuh"
+#include "decode_stream.cuh"
 #include <algorithm>
 #include <map>
 #include <stdlib.h>
@@ -26,8 +29,27 @@ struct LayerW {
     blum_q8_weight *wqkv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr, *wdown = nullptr;
 };
 
+// The batch-1 step as one persistent kernel (decode_stream.cu): stream-packed copies of the weights, the phase table and
+// the counters its grid barriers use.
+struct StreamPlan {
+    bool built = false;
+    uint64_t weights_version = 0;          // version of the model's weights the packed copy was made from
+    unsigned char* packed = nullptr;
+    DsPhase* d_phases = nullptr;
+    int nphases = 0, nstages = 0, kmax = 0, grid = 0;
+    float* part = nullptr;
+    float* attn_part = nullptr;
+    unsigned long long* ctr = nullptr;
+    size_t ctr_bytes = 0;
+};
+#define DS_MAX_SPLITS 16
+
 struct blum_llama {
     blum_llama_cfg cfg;
+    StreamPlan sp;
+    int decode_path = 0;                          // 0: persistent stream kernel when the shape allows it, 1: per-op kernels in a CUDA graph
+    int stream_state = -1;                        // -1 unknown, 0 unsupported, 1 supported
+    uint64_t weights_version = 1;
     int nq = 0, nkv = 0, ffn = 0, vocab = 0;      // local (tensor-parallel shard) sizes
     float* embed_f32 = nullptr;
     blum_q8_weight* embed_q8 = nullptr;
@@ -210,7 +232,110 @@ static int pick_nsplit(const blum_ctx* ctx, const blum_llama* m, int R, int64_t 
     return n < 1 ? 1 : n;
 }
 
-static int run_decode_step(blum_ctx* ctx, blum_llama* m, int R, int nsplit) {
+// ------------------------------------------------------------------ persistent stream kernel: plan and launch
+static bool stream_supported(blum_ctx* ctx, blum_llama* m) {
+    if (m->stream_state >= 0) return m->stream_state == 1;
+    const blum_llama_cfg& c = m->cfg;
+    const int d = c.head_dim, H = c.hidden, qd = m->nq * d;
+    bool ok = c.tp_size == 1 && c.act_dtype == BLUM_F32 && c.kv_dtype == BLUM_F32 && d == 128 && !c.embed_q8;
+    ok = ok && H % DS_UNIT_K == 0 && qd % DS_UNIT_K == 0 && m->ffn % DS_UNIT_K == 0;
+    ok = ok && ((m->nq + 2 * m->nkv) * d) % DS_UNIT_ROWS == 0 && H % DS_UNIT_ROWS == 0 && m->ffn % 8 == 0 && m->vocab % DS_UNIT_ROWS == 0;
+    int coop = 0;
+    if (ok) ok = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device) == cudaSuccess && coop != 0;
+    if (ok) {
+        const int kmax = std::max(H, std::max(qd, m->ffn));
+        const long long ring = (long long)ctx->smem_optin - 20 * 1024 - (long long)blum_ds_smem_bytes(0, kmax);
+        const int nstages = (int)std::min<long long>(DS_MAX_STAGES, ring / DS_UNIT_BYTES);
+        ok = nstages >= 4;
+        m->sp.kmax = kmax; m->sp.nstages = nstages; m->sp.grid = ctx->sm_count;
+    }
+    m->stream_state = ok ? 1 : 0;
+    return ok;
+}
+
+static void free_stream_plan(blum_llama* m) {
+    StreamPlan& sp = m->sp;
+    void* bufs[] = {sp.packed, sp.d_phases, sp.part, sp.attn_part, sp.ctr};
+    for (void* b : bufs) if (b) cudaFree(b);
+    sp.packed = nullptr; sp.d_phases = nullptr; sp.part = nullptr; sp.attn_part = nullptr; sp.ctr = nullptr;
+    sp.built = false;
+}
+
+// Packs every matrix of the model into stream units (once per set of weights) and writes the phase table.
+static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
+    StreamPlan& sp = m->sp;
+    const blum_llama_cfg& c = m->cfg;
+    const int d = c.head_dim, H = c.hidden, L = c.layers;
+    const int64_t qkv_rows = (int64_t)(m->nq + 2 * m->nkv) * d, qd = (int64_t)m->nq * d;
+    const size_t b_qkv = blum_ds_packed_bytes(qkv_rows, H), b_o = blum_ds_packed_bytes(H, qd), b_gu = blum_ds_packed_bytes(2ll * m->ffn, H),
+                 b_down = blum_ds_packed_bytes(H, m->ffn), b_head = blum_ds_packed_bytes(m->vocab, H);
+    const size_t total = (b_qkv + b_o + b_gu + b_down) * (size_t)L + b_head;
+    if (!sp.packed) {
+        cudaError_t e = cudaMalloc((void**)&sp.packed, total);
+        if (e == cudaSuccess) e = cudaMalloc((void**)&sp.d_phases, sizeof(DsPhase) * (size_t)(5 * L + 1));
+        if (e == cudaSuccess) e = cudaMalloc((void**)&sp.part, (size_t)sp.grid * 32 * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc((void**)&sp.attn_part, (size_t)m->nq * DS_MAX_SPLITS * 130 * sizeof(float));
+        sp.ctr_bytes = (size_t)(8 + sp.grid) * sizeof(unsigned long long);
+        if (e == cudaSuccess) e = cudaMalloc((void**)&sp.ctr, sp.ctr_bytes);
+        if (e != cudaSuccess) {
+            free_stream_plan(m);
+            return blum_fail(ctx, BLUM_ERR_OOM, "llama: no memory for the stream-packed weights (%zu bytes): %s", total, cudaGetErrorString(e));
+        }
+    }
+    BLUM_CUDA(ctx, cudaMemsetAsync(sp.ctr, 0, sp.ctr_bytes, ctx->stream));
+    std::vector<DsPhase> ph;
+    unsigned char* at = sp.packed;
+    auto add = [&](int kind, int layer, const blum_q8_weight* w, const blum_q8_weight* w_up, const float* norm_w, size_t bytes) -> int {
+        DsPhase P = {};
+        P.kind = kind; P.layer = layer; P.norm_w = norm_w;
+        if (w) {
+            TRY(blum_ds_pack(ctx, w, w_up, at));
+            P.w = at; P.K = (int)w->K; P.S = (int)(w->K / DS_UNIT_K); P.groups = (int)((w_up ? 2 * w->N : w->N) / DS_UNIT_ROWS);
+            at += bytes;
+        }
+        ph.push_back(P);
+        return BLUM_OK;
+    };
+    for (int l = 0; l < L; l++) {
+        const LayerW& w = m->L[l];
+        TRY(add(DS_QKV, l, w.wqkv, nullptr, w.attn_norm, b_qkv));
+        TRY(add(DS_ATTN, l, nullptr, nullptr, nullptr, 0));
+        TRY(add(DS_O, l, w.wo, nullptr, nullptr, b_o));
+        TRY(add(DS_GATEUP, l, w.wgate, w.wup, w.ffn_norm, b_gu));
+        TRY(add(DS_DOWN, l, w.wdown, nullptr, nullptr, b_down));
+    }
+    TRY(add(DS_HEAD, L, m->head, nullptr, m->out_norm, b_head));
+    sp.nphases = (int)ph.size();
+    BLUM_CUDA(ctx, cudaMemcpyAsync(sp.d_phases, ph.data(), sizeof(DsPhase) * ph.size(), cudaMemcpyHostToDevice, ctx->stream));
+    BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));      // ph is a host temporary
+    sp.built = true;
+    sp.weights_version = m->weights_version;
+    return BLUM_OK;
+}
+
+static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
+    StreamPlan& sp = m->sp;
+    if (!sp.built || sp.weights_version != m->weights_version) TRY(build_stream_plan(ctx, m));
+    const blum_llama_cfg& c = m->cfg;
+    DsParams p = {};
+    p.phases = sp.d_phases; p.nphases = sp.nphases; p.nbarriers = sp.nphases - 1;
+    p.kv = kv_view(m->kv); p.max_seqs = m->kv->max_seqs; p.max_rows = m->max_rows;
+    p.rows = m->d_rows; p.embed = m->embed_f32;
+    p.xres = (float*)m->x; p.qkv = (float*)m->qkv; p.attn = (float*)m->attn; p.mid = (float*)m->mid; p.logits = m->logits;
+    p.part = sp.part; p.attn_part = sp.attn_part; p.ctr = sp.ctr;
+    p.H = c.hidden; p.nq = m->nq; p.nkv = m->nkv; p.ffn = m->ffn; p.vocab = m->vocab;
+    // enough (head, split) items to occupy the grid once contexts are long; one split per 256 cached positions at most
+    int nsplit = (int)std::min<int64_t>(DS_MAX_SPLITS, std::max<int64_t>(1, max_ctx_len / 256));
+    p.nsplit = nsplit; p.nstages = sp.nstages; p.kmax = sp.kmax;
+    p.eps = c.rms_eps; p.scale = 1.0f / sqrtf((float)c.head_dim);
+    blum_rope_freqs(c.rope_theta, c.head_dim, &p.freqs);
+    p.err = ctx->dev_error;
+    TRY(blum_ds_launch(ctx, p));
+    return blum_argmax(ctx, m->logits, BLUM_F32, 1, m->vocab, m->d_next);
+}
+
+static int run_decode_step(blum_ctx* ctx, blum_llama* m, int R, int nsplit, int64_t max_ctx_len) {
+    if (R == 1 && m->decode_path != 1 && stream_supported(ctx, m)) return run_stream_step(ctx, m, max_ctx_len);
     auto key = std::make_pair(R, nsplit);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
@@ -285,6 +410,7 @@ int blum_llama_destroy(blum_ctx* ctx, blum_llama* m) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+    free_stream_plan(m);
     for (auto& w : m->L) {
         if (w.attn_norm) cudaFree(w.attn_norm);
         if (w.ffn_norm) cudaFree(w.ffn_norm);
@@ -396,6 +522,16 @@ const float* blum_llama_norm_weight(blum_llama* m, int layer, int which) {
     return which == 0 ? m->L[layer].attn_norm : which == 1 ? m->L[layer].ffn_norm : nullptr;
 }
 int64_t blum_llama_weight_bytes(const blum_llama* m) { return m ? m->weight_bytes : -1; }
+int blum_llama_set_decode_path(blum_ctx* ctx, blum_llama* m, int path) {
+    if (!ctx) return BLUM_ERR_INVALID;
+    BLUM_REQUIRE(ctx, m && (path == 0 || path == 1), "llama_set_decode_path: path must be 0 (automatic) or 1 (per-op kernels)");
+    m->decode_path = path;
+    return BLUM_OK;
+}
+int blum_llama_decode_path(blum_ctx* ctx, blum_llama* m) {
+    if (!ctx || !m) return BLUM_ERR_INVALID;
+    return (m->decode_path != 1 && stream_supported(ctx, m)) ? 2 : 1;
+}
 int blum_llama_set_comm(blum_ctx* ctx, blum_llama* m, blum_comm* comm) {
     if (!ctx || !m) return BLUM_ERR_INVALID;
     m->comm = comm;
@@ -405,6 +541,7 @@ int blum_llama_set_comm(blum_ctx* ctx, blum_llama* m, blum_comm* comm) {
 int blum_llama_generate_weights(blum_ctx* ctx, blum_llama* m, uint64_t seed) {
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, m != nullptr, "llama_generate_weights: null model");
+    m->weights_version++;
     std::vector<std::string> names = {"token_embd.weight", "output_norm.weight", "output.weight"};
     for (int l = 0; l < m->cfg.layers; l++) layer_names(l, &names);
     std::vector<float> host;
@@ -440,6 +577,7 @@ int blum_llama_set_tensor(blum_ctx* ctx, blum_llama* m, const char* gguf_name, c
     BLUM_REQUIRE(ctx, m && gguf_name && host_bytes, "llama_set_tensor: null argument");
     TensorRef r;
     if (!resolve_tensor(m, gguf_name, &r)) return blum_fail(ctx, BLUM_ERR_INVALID, "llama_set_tensor: unknown tensor '%s'", gguf_name);
+    m->weights_version++;                      // stream-packed copies are rebuilt before the next single-sequence step
     if (r.w) {
         BLUM_REQUIRE(ctx, is_q8_0, "llama_set_tensor: '%s' must be Q8_0", gguf_name);
         // the caller passes the FULL tensor; its row count follows from the byte count
@@ -504,6 +642,8 @@ static int finish_step(blum_ctx* ctx, blum_llama* m, const char* what) {
     if (*h_err != 0) {
         const int word = *h_err;
         BLUM_CUDA(ctx, cudaMemsetAsync(ctx->dev_error, 0, sizeof(int), ctx->stream));
+        // a stream kernel that gave up leaves its barrier counters mid-way: start the next launch from zero
+        if (m->sp.ctr) BLUM_CUDA(ctx, cudaMemsetAsync(m->sp.ctr, 0, m->sp.ctr_bytes, ctx->stream));
         return blum_fail(ctx, BLUM_ERR_DEVICE, "%s: device error word = 0x%x (bounded wait expired or bad page / sequence index)", what, word);
     }
     return BLUM_OK;
@@ -539,7 +679,7 @@ int blum_llama_decode(blum_ctx* ctx, blum_llama* m, const int32_t* seq_ids, cons
     auto roll_back = [&]() { for (int b = 0; b < grown; b++) m->kv->seq_len[seq_ids[b]] = old_len[b]; };
     if (!rc) rc = blum_kv_sync_tables(ctx, m->kv);
     if (!rc) rc = upload_rows(ctx, m, (int)B);
-    if (!rc) rc = run_decode_step(ctx, m, (int)B, pick_nsplit(ctx, m, (int)B, max_len));
+    if (!rc) rc = run_decode_step(ctx, m, (int)B, pick_nsplit(ctx, m, (int)B, max_len), max_len);
     if (!rc) {
         cudaError_t e = cudaMemcpyAsync(m->h_next, m->d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream);
         if (e == cudaSuccess && logits_out) e = cudaMemcpyAsync(logits_out, m->logits, (size_t)B * m->vocab * 4, cudaMemcpyDeviceToHost, ctx->stream);
@@ -573,7 +713,7 @@ int blum_llama_decode_loop(blum_ctx* ctx, blum_llama* m, int seq, int32_t first_
         TRY(upload_rows(ctx, m, 1));
         const int nsplit = pick_nsplit(ctx, m, 1, len + steps);
         for (int s = 0; s < steps; s++) {
-            TRY(run_decode_step(ctx, m, 1, nsplit));
+            TRY(run_decode_step(ctx, m, 1, nsplit, len + steps));
             advance_rows_kernel<<<1, 32, 0, ctx->stream>>>(m->d_rows, m->max_rows, m->d_next, m->d_hist, s, 1);
             BLUM_LAUNCH_CHECK(ctx);
         }
