@@ -364,6 +364,8 @@ int blum_llama_decode_loop(blum_ctx* ctx, blum_llama* m, int seq, int32_t first_
  * kernels.  blum_llama_decode_path returns the path a single-sequence step takes now: 2 = persistent kernel, 1 = graph. */
 int blum_llama_set_decode_path(blum_ctx* ctx, blum_llama* m, int path);
 int blum_llama_decode_path(blum_ctx* ctx, blum_llama* m);
+/* Development aid: average per-CTA cycle counters of the persistent decode kernel (see csrc/llama.cu). */
+int blum_llama_stream_profile(blum_ctx* ctx, blum_llama* m, double* out, int per_cta);
 /* Borrowed handles to the model's own tensors, for per-kernel timing: which = 0 fused q/k/v, 1 attn_output,
  * 2 ffn_gate, 3 ffn_up, 4 ffn_down, 5 output head (layer ignored).  Norm weights: 0 attn_norm, 1 ffn_norm, 2 output_norm. */
 blum_q8_weight* blum_llama_layer_weight(blum_llama* m, int layer, int which);

@@ -1,5 +1,5 @@
 // One decode step of the Llama decoder (batch 1, f32 activations and KV cache) as ONE persistent kernel with a
-// continuous weight stream.
+// continuous weight stream and data-driven hand-over between its phases.
 //
 // The reference executes a decode step as ~10^3 graph nodes, one allocation and one launch each
 // (src/graph.rs:191-224 in luminal), the quantised matmuls as one 64-thread-block matvec launch per projection
@@ -9,36 +9,38 @@
 //   * grid = one CTA per SM (cooperative launch, so all CTAs are co-resident); per matrix every CTA owns one
 //     contiguous range of 8.5 KB units (16 rows x 512 k, repacked once at load so that a unit is contiguous in
 //     HBM and already in the register layout of the MMA operand);
-//   * warp 0 is the producer: one elected thread issues cp.async.bulk copies of consecutive units into a ring of
-//     shared-memory stages (mbarrier complete_tx), limited only by free stages - it runs ahead across phase
-//     boundaries, so HBM keeps streaming while the compute warps sit in a grid barrier, stage x or run attention;
-//   * warps 1-8 consume: x is staged once per phase per CTA as block fixed point (per 32-element block
-//     x_i = xfix_i * 2^(e-21), |xfix_i| <= 2^22, split into three signed byte planes), so that the dot product of
-//     a Q8_0 block with x is exact integer arithmetic on the legacy tensor path: one mma.sync.m16n8k32.s8 covers
-//     16 rows x one block, the three planes of x are three columns of B (k is permuted inside a block so that
-//     both operands are plain 8/16-byte shared-memory loads); per (row, block): acc_plane += float(int) * (d * 2^e),
+//   * the ring: one shared-memory stage per warp.  A warp waits for its unit (mbarrier complete_tx), consumes it and
+//     at once requests the unit a whole ring further down the CTA's stream into the same stage with one
+//     cp.async.bulk - across phase boundaries, so HBM keeps streaming while the CTA waits for activations;
+//   * x is staged once per phase per CTA as block fixed point (per 32-element block x_i = xfix_i * 2^(e-21),
+//     |xfix_i| <= 2^22, split into three signed byte planes), so that the dot product of a Q8_0 block with x is
+//     exact integer arithmetic on the legacy tensor path: one mma.sync.m16n8k32.s8 covers 16 rows x one block, the
+//     three planes of x are three columns of B (k is permuted inside a block so that both operands are plain
+//     8/16-byte shared-memory loads); per (row, block): acc_plane += float(int) * (d * 2^e),
 //     result = 65536 acc_0 + 256 acc_1 + acc_2 - the block-sum-times-block-scale order of the reference kernel;
 //   * phases of a layer: [RMSNorm + q/k/v] -> [RoPE + KV append + attention] -> [o_proj + residual] ->
-//     [RMSNorm + gate/up + SwiGLU] -> [down + residual]; after the last layer [RMSNorm + LM head].  Phases are
-//     separated by grid barriers (monotonic 64-bit counter, bounded spin); a 16-row group whose k-range is cut by
-//     a CTA boundary is finished by the CTA that holds its first slice, which adds the partial sums the later
-//     CTAs publish (flag + bounded wait; the later CTAs reach those slices first, so the wait is normally over
-//     before it starts); all sums run in a fixed order, so results are reproducible bit for bit.
+//     [RMSNorm + gate/up + SwiGLU] -> [down + residual]; after the last layer [RMSNorm + LM head];
+//   * hand-over without grid barriers: every activation that crosses CTAs is a 64-bit word {f32 value, 32-bit tag},
+//     written with one store and read with one load, so a word is seen whole or not at all.  The tag names the
+//     launch and the producing phase; a reader that finds an older tag loads again (bounded).  No fence, no counter,
+//     no barrier stands between a producer's store and a consumer's load, and a CTA waits only for the values it
+//     reads.  (A buffer's next version is written two or more phases later; those writers have by then consumed
+//     values that every reader of the old version contributed to, so no reader can still be waiting for it.)
+//   * a 16-row group whose k-range is cut by a CTA boundary is finished by the CTA that holds its first slice,
+//     which adds the partial sums the later CTAs publish (tagged words again; fetched while the stream still runs);
+//     all sums run in a fixed order, so results are reproducible bit for bit.
 // Every wait is bounded by wall-clock time; on expiry the CTA raises the abort word, every later wait in the grid
-// becomes a no-op, the error word is set and the producer waits for its copies in flight before the CTA exits.
+// becomes a no-op, the error word is set, and a warp waits for its copy in flight before it exits.
 // Algorithmic bytes per launch: all Q8_0 weights of the model once (N*K*34/32 each) + the KV rows of the context.
 #include "decode_stream.cuh"
-#include <cooperative_groups.h>
 
 #define DS_TIMEOUT_NS 2000000000ull       // every wait gives up after 2 s
 #define LOG2E 1.4426950408889634f
+#define DS_STAGE_UNROLL 4
 
 __device__ __forceinline__ uint32_t ds_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ds_mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ds_smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void ds_mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ds_smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void ds_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ds_smem_u32(bar)), "r"(bytes) : "memory");
@@ -49,24 +51,40 @@ __device__ __forceinline__ bool ds_mbar_try(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(ds_smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void ds_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(ds_smem_u32(dst)), "l"(src), "r"(bytes), "r"(ds_smem_u32(bar)) : "memory");
+// weights are read once: their lines are the first to leave L2 again
+__device__ __forceinline__ void ds_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(ds_smem_u32(dst)), "l"(src), "r"(bytes), "r"(ds_smem_u32(bar)), "l"(policy) : "memory");
 }
-__device__ __forceinline__ unsigned long long ds_ld_acquire(const unsigned long long* p) {
+__device__ __forceinline__ void ds_bulk_prefetch(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+// tagged words: {value, tag} in one naturally aligned 64-bit access
+__device__ __forceinline__ void ds_st_tagged(unsigned long long* p, float v, uint32_t tag) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ds_ld_word(const unsigned long long* p) {
     unsigned long long v;
-    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void ds_st_release(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ ulonglong2 ds_ld_word2(const unsigned long long* p) {
+    ulonglong2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+    return v;
 }
-__device__ __forceinline__ void ds_named_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DS_CONSUMER_THREADS) : "memory"); }
+__device__ __forceinline__ uint32_t ds_tag_of(unsigned long long w) { return (uint32_t)(w >> 32); }
+__device__ __forceinline__ float ds_val_of(unsigned long long w) { return __uint_as_float((uint32_t)w); }
 
-// records a timeout: error word for the host, abort word for every other CTA, abort flag for this CTA
-__device__ __noinline__ void ds_give_up(int* err, unsigned long long* ctr, volatile int* s_abort) {
+// The first wait that gives up also records where: ctr[3] = site (1 weight stage, 2 activation word, 3 attention
+// input, 4 partial sums of a split group), ctr[4] = CTA, ctr[5], ctr[6] = what it waited for and what it saw.
+__device__ __noinline__ void ds_give_up(int* err, unsigned long long* ctr, volatile int* s_abort, int site, long long a, long long b) {
     *s_abort = 1;
     atomicOr(err, 0x400);
+    if (atomicCAS(ctr + 3, 0ull, (unsigned long long)site) == 0ull) {
+        ctr[4] = blockIdx.x; ctr[5] = (unsigned long long)a; ctr[6] = (unsigned long long)b;
+    }
     atomicExch(ctr + 2, 1ull);
 }
 __device__ __forceinline__ bool ds_aborted(const DsParams& p, volatile int* s_abort) {
@@ -75,7 +93,7 @@ __device__ __forceinline__ bool ds_aborted(const DsParams& p, volatile int* s_ab
     return false;
 }
 // bounded wait on an mbarrier phase; a no-op once the grid has aborted
-__device__ __forceinline__ void ds_mbar_wait(uint64_t* bar, uint32_t parity, const DsParams& p, volatile int* s_abort) {
+__device__ __forceinline__ void ds_mbar_wait(uint64_t* bar, uint32_t parity, const DsParams& p, volatile int* s_abort, int site, long long what) {
     if (*s_abort) return;
     if (ds_mbar_try(bar, parity)) return;
     const unsigned long long t0 = blum_globaltimer();
@@ -83,75 +101,75 @@ __device__ __forceinline__ void ds_mbar_wait(uint64_t* bar, uint32_t parity, con
         if (ds_mbar_try(bar, parity)) return;
         if ((spin & 63u) == 0u) {
             if (ds_aborted(p, s_abort)) return;
-            if (blum_globaltimer() - t0 > DS_TIMEOUT_NS) { ds_give_up(p.err, p.ctr, s_abort); return; }
+            if (blum_globaltimer() - t0 > DS_TIMEOUT_NS) { ds_give_up(p.err, p.ctr, s_abort, site, what, parity); return; }
         }
     }
 }
-// bounded wait until *word >= target (acquire)
-__device__ __forceinline__ void ds_wait_ge(const unsigned long long* word, unsigned long long target, const DsParams& p,
-                                           volatile int* s_abort) {
-    if (*s_abort) return;
-    if (ds_ld_acquire(word) >= target) return;
+// bounded wait for a tagged word; returns the word (whatever it holds once the grid has aborted)
+__device__ __forceinline__ unsigned long long ds_wait_word(const unsigned long long* ptr, uint32_t tag, const DsParams& p,
+                                                           volatile int* s_abort, int site) {
+    unsigned long long w = ds_ld_word(ptr);
+    if (ds_tag_of(w) == tag || *s_abort) return w;
     const unsigned long long t0 = blum_globaltimer();
     for (uint32_t spin = 1;; spin++) {
-        if (ds_ld_acquire(word) >= target) return;
-        if (spin > 16u) __nanosleep(32);
+        w = ds_ld_word(ptr);
+        if (ds_tag_of(w) == tag) return w;
         if ((spin & 63u) == 0u) {
-            if (ds_aborted(p, s_abort)) return;
-            if (blum_globaltimer() - t0 > DS_TIMEOUT_NS) { ds_give_up(p.err, p.ctr, s_abort); return; }
+            if (ds_aborted(p, s_abort)) return w;
+            if (blum_globaltimer() - t0 > DS_TIMEOUT_NS) { ds_give_up(p.err, p.ctr, s_abort, site, (long long)tag, (long long)ds_tag_of(w)); return w; }
         }
     }
 }
-
-// grid barrier of the compute warps (the producer warp does not take part: its schedule is static)
-__device__ __forceinline__ void ds_grid_sync(const DsParams& p, unsigned long long target, int tid_c, volatile int* s_abort) {
-    ds_named_sync();
-    if (tid_c == 0 && !*s_abort) {
-        __threadfence();
-        atomicAdd(p.ctr, 1ull);
-        ds_wait_ge(p.ctr, target, p, s_abort);
-        __threadfence();
-    }
-    ds_named_sync();
+__device__ __forceinline__ float ds_wait_value(const unsigned long long* ptr, uint32_t tag, const DsParams& p, volatile int* s_abort, int site) {
+    return ds_val_of(ds_wait_word(ptr, tag, p, s_abort, site));
 }
 
-__device__ __forceinline__ float4 ds_ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void ds_sync() { __syncthreads(); }
+__device__ __forceinline__ int ds_sync_and(int pred) { return __syncthreads_and(pred); }
 
 struct DsShared {
-    uint64_t full[DS_MAX_STAGES], empty[DS_MAX_STAGES];
-    float4 red[2][DS_CONSUMER_WARPS][32];           // cross-warp reduction of a group segment, double buffered
-    float wred[DS_CONSUMER_WARPS];                  // sum of squares per warp
+    uint64_t full[DS_STAGES];
+    float partial[DS_PARTIAL_SLOTS][16];            // per-unit row sums waiting for the rest of their group
+    int gcnt[DS_PARTIAL_SLOTS];                     // units of a group deposited so far (indexed by group % slots)
+    float wred[DS_WARPS];                           // sum of squares per warp
     float q[128], knew[128], vnew[128];
+    float rsn[64], rcs[64];                         // rotation of the step's position
     float sc[DS_ATTN_TILE];
     long long koff[DS_ATTN_TILE];
-    float o_half[2][128];
-    float l_half[2];
+    float o_part[DS_ATTN_PARTS][128];
+    float l_part[DS_ATTN_PARTS];
     unsigned long long seq;
     int abort;
+    float resid[DS_RESIDUAL_ROWS];                  // residual rows of the groups this CTA finishes (o_proj / down)
+    float pp_sum[16];                               // partial sums of the later CTAs for this CTA's last group
+    int pp_state;                                   // 1: pp_sum is valid
+    int2 range[DS_MAX_PHASES];                      // this CTA's units [x, y) of every phase
 };
+
+// tag of what phase `ph` of launch `seq` writes (ph = -1: the embedding row that CTA 0 copies into the residual stream)
+__device__ __forceinline__ uint32_t ds_tag(unsigned long long seq, int nphases, int ph) {
+    return (uint32_t)((seq + 1ull) * (unsigned long long)(nphases + 2) + (unsigned long long)(ph + 1));
+}
 
 // ---- x of a phase -> block fixed point in shared memory (three signed byte planes + one scale per 32 elements)
 // planes: [K/32][3][32] bytes; scales: [K/32] floats.  Returns rsqrt(mean(x^2) + eps) when a norm weight is folded in.
-__device__ __forceinline__ float ds_stage_x(const DsParams& p, const DsPhase& P, DsShared& sh, unsigned char* xpl, float* xsc,
-                                            int tid_c, int cta) {
+// x is the previous phase's output: tagged words that are loaded again until they carry that phase's tag.
+__device__ __forceinline__ float ds_stage_x(const DsParams& p, const DsPhase& P, int ph, unsigned long long seq, DsShared& sh,
+                                            unsigned char* xpl, float* xsc, int tid_c, volatile int* s_abort) {
     const int K = P.K, lane = tid_c & 31, cw = tid_c >> 5;
-    const float* src;
-    bool copy_to_xres = false;
-    if (P.kind == DS_QKV) {
-        if (P.layer == 0) {
-            int id = p.rows[0];
-            if (id < 0 || id >= p.vocab) { if (tid_c == 0) atomicOr(p.err, 0x100); id = 0; }
-            src = p.embed + (size_t)id * p.H;
-            copy_to_xres = (cta == 0);
-        } else src = p.xres;
-    } else if (P.kind == DS_O) src = p.attn;
-    else if (P.kind == DS_DOWN) src = p.mid;
-    else src = p.xres;
+    const uint32_t tag = ds_tag(seq, p.nphases, ph - 1);
+    const unsigned long long* src = P.kind == DS_O ? p.attn : P.kind == DS_DOWN ? p.mid : p.xres;
+    const bool from_embed = (P.kind == DS_QKV && P.layer == 0);
     const bool combine = (P.kind == DS_O) && p.nsplit > 1;
+    const float* erow = nullptr;
+    if (from_embed) {
+        int id = p.rows[0];
+        if (id < 0 || id >= p.vocab) { if (tid_c == 0) atomicOr(p.err, 0x100); id = 0; }
+        erow = p.embed + (size_t)id * p.H;
+    }
     float ss = 0.f;
     // one step of four consecutive elements: norm weight, block maximum over the 8 lanes of a 32-element block, digits
     auto put = [&](float (&v)[4], int k) {
-        if (copy_to_xres) *reinterpret_cast<float4*>(p.xres + k) = make_float4(v[0], v[1], v[2], v[3]);
         ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
         if (P.norm_w) {
             const float4 nw = __ldg(reinterpret_cast<const float4*>(P.norm_w + k));
@@ -183,36 +201,58 @@ __device__ __forceinline__ float ds_stage_x(const DsParams& p, const DsPhase& P,
         *reinterpret_cast<unsigned*>(blk + 64) = pc;
         if ((k & 31) == 0) xsc[k >> 5] = down;
     };
-    if (!combine) {
-        constexpr int STEP = DS_CONSUMER_THREADS * 4;
-        for (int k0 = tid_c * 4; k0 < K; k0 += STEP * 8) {       // the loads of eight steps are in flight together
-            float4 buf[8];
+    constexpr int STEP = DS_THREADS * 4;
+    if (from_embed) {
+        // layer 0 reads the embedding row itself
+        for (int k = tid_c * 4; k < K; k += STEP) {
+            const float4 e = __ldg(reinterpret_cast<const float4*>(erow + k));
+            float v[4] = {e.x, e.y, e.z, e.w};
+            put(v, k);
+        }
+    } else if (!combine) {
+        for (int kb = 0; kb < K; kb += STEP * DS_STAGE_UNROLL) {               // (every thread runs every batch: the batch votes)
+            const int k0 = kb + tid_c * 4;
+            ulonglong2 buf[DS_STAGE_UNROLL][2];
+            // All words of the batch are requested together, and those that still carry an older tag are requested together
+            // again: one round trip per attempt, however many of them are late.
+            unsigned ready = 0;
+            const unsigned long long t0 = blum_globaltimer();
+            for (uint32_t spin = 0;; spin++) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) if (k0 + i * STEP < K) buf[i] = ds_ldcg4(src + k0 + i * STEP);
+                for (int i = 0; i < DS_STAGE_UNROLL; i++)
+                    if (k0 + i * STEP < K && !((ready >> i) & 1u)) { buf[i][0] = ds_ld_word2(src + k0 + i * STEP); buf[i][1] = ds_ld_word2(src + k0 + i * STEP + 2); }
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (k0 + i * STEP < K) {
-                    float v[4] = {buf[i].x, buf[i].y, buf[i].z, buf[i].w};
-                    put(v, k0 + i * STEP);
+                for (int i = 0; i < DS_STAGE_UNROLL; i++)
+                    if (k0 + i * STEP >= K || (ds_tag_of(buf[i][0].x) == tag && ds_tag_of(buf[i][0].y) == tag && ds_tag_of(buf[i][1].x) == tag && ds_tag_of(buf[i][1].y) == tag))
+                        ready |= 1u << i;
+                if (ds_sync_and(ready == (1u << DS_STAGE_UNROLL) - 1u || *s_abort)) break;      // the same answer in every thread
+                if (tid_c == 0 && (spin & 15u) == 15u && !ds_aborted(p, s_abort) && blum_globaltimer() - t0 > DS_TIMEOUT_NS)
+                    ds_give_up(p.err, p.ctr, s_abort, 2, (long long)tag, (long long)k0);
+            }
+#pragma unroll
+            for (int i = 0; i < DS_STAGE_UNROLL; i++) {
+                const int k = k0 + i * STEP;
+                if (k < K) {
+                    float v[4] = {ds_val_of(buf[i][0].x), ds_val_of(buf[i][0].y), ds_val_of(buf[i][1].x), ds_val_of(buf[i][1].y)};
+                    put(v, k);
                 }
             }
         }
     } else {
-        for (int k = tid_c * 4; k < K; k += DS_CONSUMER_THREADS * 4) {
+        for (int k = tid_c * 4; k < K; k += STEP) {
             // merge the split attention partials of head k/128: weights exp2((m_s - m_max) log2 e)
             const int h = k >> 7, c = k & 127;
-            const float* base = p.attn_part + (size_t)h * p.nsplit * 130;
+            const unsigned long long* base = p.attn_part + (size_t)h * p.nsplit * 130;
             float mmax = -INFINITY;
-            for (int s = 0; s < p.nsplit; s++) mmax = fmaxf(mmax, __ldcg(base + s * 130 + 128));
+            for (int s = 0; s < p.nsplit; s++) mmax = fmaxf(mmax, ds_wait_value(base + s * 130 + 128, tag, p, s_abort, 2));
             float den = 0.f;
             float v[4] = {0.f, 0.f, 0.f, 0.f};
             for (int s = 0; s < p.nsplit; s++) {
-                const float ms = __ldcg(base + s * 130 + 128);
+                const float ms = ds_wait_value(base + s * 130 + 128, tag, p, s_abort, 2);
                 const float w = (ms == -INFINITY) ? 0.f : exp2f((ms - mmax) * LOG2E);
-                den = fmaf(__ldcg(base + s * 130 + 129), w, den);
-                const float2 o01 = __ldcg(reinterpret_cast<const float2*>(base + s * 130 + c));
-                const float2 o23 = __ldcg(reinterpret_cast<const float2*>(base + s * 130 + c + 2));
-                v[0] = fmaf(o01.x, w, v[0]); v[1] = fmaf(o01.y, w, v[1]); v[2] = fmaf(o23.x, w, v[2]); v[3] = fmaf(o23.y, w, v[3]);
+                den = fmaf(ds_wait_value(base + s * 130 + 129, tag, p, s_abort, 2), w, den);
+#pragma unroll
+                for (int e = 0; e < 4; e++) v[e] = fmaf(ds_wait_value(base + s * 130 + c + e, tag, p, s_abort, 2), w, v[e]);
             }
             const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll
@@ -224,103 +264,141 @@ __device__ __forceinline__ float ds_stage_x(const DsParams& p, const DsPhase& P,
         ss = warp_sum(ss);
         if (lane == 0) sh.wred[cw] = ss;
     }
-    ds_named_sync();
+    ds_sync();
     float rs = 1.f;
     if (P.norm_w) {
         float s = 0.f;
 #pragma unroll
-        for (int w = 0; w < DS_CONSUMER_WARPS; w++) s += sh.wred[w];
+        for (int w = 0; w < DS_WARPS; w++) s += sh.wred[w];
         rs = rsqrtf(s / (float)K + p.eps);
     }
     return rs;
 }
 
-// ---- RoPE + KV append + attention of the new token; items (q head, split) are dealt round robin to the CTAs
-__device__ __forceinline__ void ds_attention(const DsParams& p, int layer, DsShared& sh, int tid_c, int cta, int ncta,
-                                             volatile int* s_abort) {
-    const int lane = tid_c & 31, cw = tid_c >> 5;
-    const KvView& kv = p.kv;
-    const int ps = kv.page_size, G = p.nq / p.nkv;
-    int seq = p.rows[p.max_rows], ctx = p.rows[3 * p.max_rows];
-    if (seq < 0 || seq >= p.max_seqs || ctx < 1 || (ctx + ps - 1) / ps > kv.max_pages_per_seq) {
+// (sequence, context length) of the step, validated
+__device__ __forceinline__ void ds_step_row(const DsParams& p, int tid_c, int& seq, int& ctx) {
+    seq = p.rows[p.max_rows]; ctx = p.rows[3 * p.max_rows];
+    const int ps = p.kv.page_size;
+    if (seq < 0 || seq >= p.max_seqs || ctx < 1 || (ctx + ps - 1) / ps > p.kv.max_pages_per_seq) {
         if (tid_c == 0) atomicOr(p.err, 0x100);
         seq = 0; ctx = 1;
     }
+}
+// cached positions [c0, c1) of split `split` (split on page boundaries)
+__device__ __forceinline__ void ds_split_range(const DsParams& p, int pos, int split, int& c0, int& c1) {
+    const int ps = p.kv.page_size;
+    const int npages = (pos + ps - 1) / ps, pages_per_split = (npages + p.nsplit - 1) / p.nsplit;
+    c0 = min(pos, split * pages_per_split * ps); c1 = min(pos, (split + 1) * pages_per_split * ps);
+}
+// row offsets of tile [t0, t0 + n) of kv head kvh into koff
+__device__ __forceinline__ void ds_tile_offsets(const DsParams& p, DsShared& sh, int layer, const int32_t* table, int kvh, int t0, int n, int tid_c) {
+    if (tid_c < n) {
+        const int pj = t0 + tid_c, ps = p.kv.page_size;
+        int32_t page = table[pj / ps];
+        if (page < 0 || page >= p.kv.num_pages) { atomicOr(p.err, 0x200); page = 0; }
+        sh.koff[tid_c] = kv_tile_offset(p.kv, layer, page, 0, kvh, pj % ps);
+    }
+}
+
+// ---- RoPE + KV append + attention of the new token; items (q head, split) are dealt round robin to the CTAs
+__device__ __forceinline__ void ds_attention(const DsParams& p, int layer, int ph, unsigned long long seqno, DsShared& sh, int tid_c,
+                                             int cta, int ncta, volatile int* s_abort) {
+    const int nitems = p.nq * p.nsplit;
+    if (cta >= nitems) return;
+    const int lane = tid_c & 31, cw = tid_c >> 5;
+    const KvView& kv = p.kv;
+    const int ps = kv.page_size, G = p.nq / p.nkv;
+    const uint32_t tag_in = ds_tag(seqno, p.nphases, ph - 1), tag_out = ds_tag(seqno, p.nphases, ph);
+    int seq, ctx;
+    ds_step_row(p, tid_c, seq, ctx);
     const int pos = ctx - 1;
     const int32_t* table = kv.table + (size_t)seq * kv.max_pages_per_seq;
     float* pool = reinterpret_cast<float*>(kv.pool);
     const long long vdelta = (long long)kv.kv_heads * ps * 128;       // K tile -> V tile of the same (page, head)
-    const int hh = tid_c >> 7, c = tid_c & 127;
-    const int nitems = p.nq * p.nsplit;
+    const int part = tid_c >> 7, c = tid_c & 127;                     // partition of the positions for P V, and the dim
+    if (tid_c < 64) {
+        const float a = (float)pos * p.freqs.inv_freq[tid_c];
+        sh.rsn[tid_c] = sinf(a); sh.rcs[tid_c] = sinf(1.5707964f - a);   // cos(x) = sin(pi/2 - x), as the reference computes it
+    }
     for (int item = cta; item < nitems; item += ncta) {
         const int h = item % p.nq, split = item / p.nq, kvh = h / G;
+        int c0, c1;
+        ds_split_range(p, pos, split, c0, c1);
+        // Nothing up to here depends on the new token: the row offsets of the first tile, and L2 prefetches of its cached
+        // K and V rows (the weight stream has long pushed them out of L2), go out before q/k/v are waited for.
+        if (c1 > c0) {
+            const int n0 = min(DS_ATTN_TILE, c1 - c0);
+            ds_tile_offsets(p, sh, layer, table, kvh, c0, n0, tid_c);
+            if (tid_c < n0) {
+                const float* kr = pool + sh.koff[tid_c];
+#pragma unroll
+                for (int l = 0; l < 4; l++) {                                    // a row of 128 floats is four 128-byte lines
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(kr + l * 32));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(kr + vdelta + l * 32));
+                }
+            }
+        }
+        ds_sync();                                                  // rsn / rcs / koff are written
         // rotary embedding of q (threads 0..63) and of the new k (64..127); v is copied (128..255)
         if (tid_c < 128) {
             const int pi = tid_c & 63;
-            const float a = (float)pos * p.freqs.inv_freq[pi];
-            const float sn = sinf(a), cs = sinf(1.5707964f - a);       // cos(x) = sin(pi/2 - x), as the reference computes it
-            const float* s2 = p.qkv + (size_t)((tid_c < 64) ? h : p.nq + kvh) * 128 + 2 * pi;
-            const float2 x = __ldcg(reinterpret_cast<const float2*>(s2));
+            const float sn = sh.rsn[pi], cs = sh.rcs[pi];
+            const unsigned long long* s2 = p.qkv + (size_t)((tid_c < 64) ? h : p.nq + kvh) * 128 + 2 * pi;
+            ulonglong2 w = ds_ld_word2(s2);
+            if (ds_tag_of(w.x) != tag_in) w.x = ds_wait_word(s2, tag_in, p, s_abort, 3);
+            if (ds_tag_of(w.y) != tag_in) w.y = ds_wait_word(s2 + 1, tag_in, p, s_abort, 3);
+            const float x0 = ds_val_of(w.x), x1 = ds_val_of(w.y);
             float* dst = (tid_c < 64) ? sh.q : sh.knew;
-            dst[2 * pi] = x.x * cs - x.y * sn;
-            dst[2 * pi + 1] = x.x * sn + x.y * cs;
-        } else {
-            sh.vnew[c] = __ldcg(p.qkv + (size_t)(p.nq + p.nkv + kvh) * 128 + c);
+            dst[2 * pi] = x0 * cs - x1 * sn;
+            dst[2 * pi + 1] = x0 * sn + x1 * cs;
+        } else if (tid_c < 256) {
+            sh.vnew[c] = ds_wait_value(p.qkv + (size_t)(p.nq + p.nkv + kvh) * 128 + c, tag_in, p, s_abort, 3);
         }
-        ds_named_sync();
-        if (split == 0 && h % G == 0) {     // one item per kv head appends the new row to its page slot
+        ds_sync();
+        if (split == 0 && h % G == 0 && tid_c < 256) {     // one item per kv head appends the new row to its page slot
             const int32_t page = table[pos / ps];
             if (page < 0 || page >= kv.num_pages) { if (tid_c == 0) atomicOr(p.err, 0x40); }
             else {
                 const long long o = kv_tile_offset(kv, layer, page, 0, kvh, pos % ps);
-                if (hh == 0) pool[o + c] = sh.knew[c]; else pool[o + vdelta + c] = sh.vnew[c];
+                if (part == 0) pool[o + c] = sh.knew[c]; else pool[o + vdelta + c] = sh.vnew[c];
             }
         }
         const float4 q4 = *reinterpret_cast<const float4*>(&sh.q[lane * 4]);
-        // cached positions [0, pos) split on page boundaries
-        const int npages = (pos + ps - 1) / ps, pages_per_split = (npages + p.nsplit - 1) / p.nsplit;
-        const int c0 = min(pos, split * pages_per_split * ps), c1 = min(pos, (split + 1) * pages_per_split * ps);
         float m_run = -INFINITY, l_run = 0.f, o_acc = 0.f;
         for (int t0 = c0; t0 < c1; t0 += DS_ATTN_TILE) {
             const int n = min(DS_ATTN_TILE, c1 - t0);
-            if (tid_c < n) {
-                const int pj = t0 + tid_c;
-                int32_t page = table[pj / ps];
-                if (page < 0 || page >= kv.num_pages) { atomicOr(p.err, 0x200); page = 0; }
-                sh.koff[tid_c] = kv_tile_offset(kv, layer, page, 0, kvh, pj % ps);
-            }
-            ds_named_sync();
-            for (int j0 = cw; j0 < n; j0 += DS_CONSUMER_WARPS * 4) {       // four independent rows per warp in flight
+            if (t0 > c0) { ds_tile_offsets(p, sh, layer, table, kvh, t0, n, tid_c); ds_sync(); }
+            for (int j0 = cw; j0 < n; j0 += DS_WARPS * 4) {               // four independent rows per warp in flight
                 float4 kr[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const int j = j0 + i * DS_CONSUMER_WARPS;
+                    const int j = j0 + i * DS_WARPS;
                     kr[i] = (j < n) ? __ldg(reinterpret_cast<const float4*>(pool + sh.koff[j]) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const int j = j0 + i * DS_CONSUMER_WARPS;
+                    const int j = j0 + i * DS_WARPS;
                     const float dot = warp_sum(kr[i].x * q4.x + kr[i].y * q4.y + kr[i].z * q4.z + kr[i].w * q4.w);
                     if (lane == 0 && j < n) sh.sc[j] = dot * p.scale;
                 }
             }
-            ds_named_sync();
+            ds_sync();
             float mx = -INFINITY;
             for (int j = lane; j < n; j += 32) mx = fmaxf(mx, sh.sc[j]);
             mx = warp_max(mx);
             const float m_new = fmaxf(m_run, mx);
             const float corr = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * LOG2E);
-            ds_named_sync();                                               // every warp has read the raw scores
+            ds_sync();                                               // every warp has read the raw scores
             if (tid_c < n) sh.sc[tid_c] = exp2f((sh.sc[tid_c] - m_new) * LOG2E);
-            ds_named_sync();
+            ds_sync();
             o_acc *= corr; l_run *= corr; m_run = m_new;
 #pragma unroll 8
-            for (int j = hh; j < n; j += 2) {
+            for (int j = part; j < n; j += DS_ATTN_PARTS) {
                 const float pj = sh.sc[j];
                 o_acc = fmaf(pj, __ldg(pool + sh.koff[j] + vdelta + c), o_acc);
                 l_run += pj;
             }
-            ds_named_sync();                                               // sc / koff are rewritten by the next tile
+            ds_sync();                                               // sc / koff are rewritten by the next tile
         }
         if (split == 0) {       // the new token itself: its k and v are still in shared memory
             const float4 k4 = *reinterpret_cast<const float4*>(&sh.knew[lane * 4]);
@@ -329,194 +407,310 @@ __device__ __forceinline__ void ds_attention(const DsParams& p, int layer, DsSha
             const float corr = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * LOG2E);
             const float pj = exp2f((s - m_new) * LOG2E);
             o_acc *= corr; l_run *= corr; m_run = m_new;
-            if (hh == 0) { o_acc = fmaf(pj, sh.vnew[c], o_acc); l_run += pj; }
+            if (part == 0) { o_acc = fmaf(pj, sh.vnew[c], o_acc); l_run += pj; }
         }
-        sh.o_half[hh][c] = o_acc;
-        if (c == 0) sh.l_half[hh] = l_run;
-        ds_named_sync();
-        if (hh == 0) {
-            const float o = sh.o_half[0][c] + sh.o_half[1][c], l = sh.l_half[0] + sh.l_half[1];
-            if (p.nsplit == 1) p.attn[(size_t)h * 128 + c] = o * (l > 0.f ? 1.f / l : 0.f);
+        sh.o_part[part][c] = o_acc;
+        if (c == 0) sh.l_part[part] = l_run;
+        ds_sync();
+        if (part == 0) {
+            float o = 0.f, l = 0.f;
+#pragma unroll
+            for (int i = 0; i < DS_ATTN_PARTS; i++) { o += sh.o_part[i][c]; l += sh.l_part[i]; }
+            if (p.nsplit == 1) ds_st_tagged(p.attn + (size_t)h * 128 + c, o * (l > 0.f ? 1.f / l : 0.f), tag_out);
             else {
-                float* dst = p.attn_part + ((size_t)h * p.nsplit + split) * 130;
-                dst[c] = o;
-                if (c == 0) { dst[128] = m_run; dst[129] = l; }
+                unsigned long long* dst = p.attn_part + ((size_t)h * p.nsplit + split) * 130;
+                ds_st_tagged(dst + c, o, tag_out);
+                if (c == 0) { ds_st_tagged(dst + 128, m_run, tag_out); ds_st_tagged(dst + 129, l, tag_out); }
             }
         }
-        ds_named_sync();                                                   // shared scratch is reused by the next item
+        ds_sync();                                                   // shared scratch is reused by the next item
     }
-    (void)s_abort;
+}
+
+// position of a CTA in its static weight stream (the units of all phases, in phase order)
+struct DsCursor {
+    int ph, u, u1;
+    const unsigned char* base;
+};
+// first and one-past-last unit of CTA `cta` among `units` (an even split of the unit list over the grid)
+__device__ __forceinline__ int ds_range_lo(int units, int cta, int ncta) { return (int)(((unsigned long long)(unsigned)units * (unsigned)cta) / (unsigned)ncta); }
+__device__ __forceinline__ void ds_cursor_seek(const DsPhase* phases, int nphases, const DsShared& sh, DsCursor& c) {   // first unit at or after phase c.ph
+    for (; c.ph < nphases; c.ph++) {
+        const int2 r = sh.range[c.ph];
+        if (r.x < r.y) { c.u = r.x; c.u1 = r.y; c.base = phases[c.ph].w; return; }
+    }
+    c.u = c.u1 = 0; c.base = nullptr;
+}
+__device__ __forceinline__ void ds_cursor_advance(const DsPhase* phases, int nphases, const DsShared& sh, DsCursor& c, int k) {
+    while (k > 0 && c.base) {
+        const int avail = c.u1 - c.u;
+        if (k < avail) { c.u += k; k = 0; }
+        else { k -= avail; c.ph++; ds_cursor_seek(phases, nphases, sh, c); }
+    }
+}
+
+// Partial sums of the later CTAs that hold slices of the group ending at unit `gend` (whose first slices this CTA holds),
+// added in CTA order.  `block` = false only looks: returns false if one of them has not been published yet.
+__device__ __forceinline__ bool ds_fetch_partners(const DsParams& p, int units, int gend, int cta, int ncta, uint32_t tag, int lane,
+                                                  bool block, volatile int* s_abort, float& sum) {
+    sum = 0.f;
+    for (int c2 = cta + 1; c2 < ncta; c2++) {
+        const int r0 = ds_range_lo(units, c2, ncta), r1 = ds_range_lo(units, c2 + 1, ncta);
+        if (r0 >= gend) break;
+        if (r1 <= r0) continue;
+        const unsigned long long* src = p.part + (size_t)c2 * 16 + (lane & 15);
+        unsigned long long w = block ? ds_wait_word(src, tag, p, s_abort, 4) : ds_ld_word(src);
+        if (!__all_sync(0xffffffffu, ds_tag_of(w) == tag || *s_abort)) return false;
+        sum += ds_val_of(w);
+    }
+    return true;
 }
 
 __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __grid_constant__ DsParams p) {
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ __align__(16) DsShared sh;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid_c = threadIdx.x, cw = tid_c >> 5, lane = tid_c & 31;
     const int cta = blockIdx.x, ncta = gridDim.x;
-    const int NS = p.nstages;
+    constexpr int NS = DS_STAGES;
     unsigned char* ring = dyn;
     unsigned char* xpl = dyn + (size_t)NS * DS_UNIT_BYTES;
     float* xsc = reinterpret_cast<float*>(xpl + (size_t)p.kmax * 3);
     volatile int* s_abort = &sh.abort;
 
-    if (tid == 0) {
-        for (int s = 0; s < NS; s++) { ds_mbar_init(&sh.full[s], 1); ds_mbar_init(&sh.empty[s], DS_CONSUMER_WARPS); }
+    // the phase table and this CTA's share of every phase's units: read all the time, so they live in shared memory
+    DsPhase* phases = reinterpret_cast<DsPhase*>(xsc + p.kmax / 32);
+    for (int i = tid_c; i < p.nphases; i += DS_THREADS) {
+        const DsPhase P = p.phases[i];
+        phases[i] = P;
+        // short phases hand out whole 16-row groups (a group cut between two CTAs costs a round trip at the very end of the
+        // phase, more than the uneven share does); long ones are cut to the unit
+        if (!P.w) sh.range[i] = make_int2(0, 0);
+        else if (P.whole) sh.range[i] = make_int2(ds_range_lo(P.groups, cta, ncta) * P.S, ds_range_lo(P.groups, cta + 1, ncta) * P.S);
+        else sh.range[i] = make_int2(ds_range_lo(P.groups * P.S, cta, ncta), ds_range_lo(P.groups * P.S, cta + 1, ncta));
+    }
+    if (tid_c == 0) {
+        for (int s = 0; s < NS; s++) ds_mbar_init(&sh.full[s], 1);
         sh.abort = 0;
         sh.seq = *reinterpret_cast<volatile unsigned long long*>(p.ctr + 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (int i = tid_c; i < DS_PARTIAL_SLOTS; i += DS_THREADS) sh.gcnt[i] = 0;
     __syncthreads();
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ producer: the static weight stream
-        if (lane == 0) {
-            int slot = 0;
-            uint32_t wrap = 0;           // completed passes over the ring
-            long long issued = 0;
-            bool stop = false;
-            for (int ph = 0; ph < p.nphases && !stop; ph++) {
-                const DsPhase P = p.phases[ph];
-                if (!P.w) continue;
-                const long long units = (long long)P.groups * P.S;
-                const long long u0 = units * cta / ncta, u1 = units * (cta + 1) / ncta;
-                const unsigned char* src = P.w + (size_t)u0 * DS_UNIT_BYTES;
-                for (long long u = u0; u < u1; u++, src += DS_UNIT_BYTES) {
-                    if (wrap > 0) ds_mbar_wait(&sh.empty[slot], (wrap - 1) & 1u, p, s_abort);
-                    if (*s_abort) { stop = true; break; }
-                    ds_mbar_expect_tx(&sh.full[slot], DS_UNIT_BYTES);
-                    ds_bulk_load(ring + (size_t)slot * DS_UNIT_BYTES, src, DS_UNIT_BYTES, &sh.full[slot]);
-                    issued++;
-                    if (++slot == NS) { slot = 0; wrap++; }
-                }
-            }
-            if (stop) {
-                // aborted: wait (bounded) for the copies still in flight before this CTA's shared memory is released
-                const long long back = issued < NS ? issued : NS;
-                int s2 = slot; uint32_t w2 = wrap;
-                for (long long i = 0; i < back; i++) {
-                    if (--s2 < 0) { s2 = NS - 1; w2--; }
-                    const unsigned long long t0 = blum_globaltimer();
-                    while (!ds_mbar_try(&sh.full[s2], w2 & 1u) && blum_globaltimer() - t0 < DS_TIMEOUT_NS) {}
-                }
-            }
+    // ---- the weight stream.  Unit number n of this CTA's stream (all phases, in order) lives in ring stage n % NS, and
+    // stage i belongs to warp i: the warp waits for the unit, consumes it and at once requests unit n + NS into the same
+    // stage with one bulk copy (mbarrier complete_tx).  The requests of a warp therefore run ahead of its compute by a
+    // whole ring, across phase boundaries: while the CTA waits for activations or runs attention, the next phase's first
+    // units are landing.  (A stage has a single consumer, so that consumer sees every phase of the stage's barrier in
+    // order and no "stage free" barrier is needed.)
+    DsCursor rf = {0, 0, 0, nullptr};             // the unit this warp requests next
+    ds_cursor_seek(phases, p.nphases, sh, rf);
+    ds_cursor_advance(phases, p.nphases, sh, rf, cw);
+    bool outstanding = false;                     // a copy into this warp's stage is in flight or unconsumed
+    int rf_n = cw, req_n = 0;                     // stream numbers of `rf` and of the outstanding request
+    int pf_n = -1;                                // highest stream number this warp has pulled into L2
+    uint64_t evict_first;                         // weights are read once: their lines leave L2 first
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(evict_first));
+    auto request = [&]() {                        // lane 0 only
+        if (rf.base && !*s_abort) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the stage was last read through the generic proxy
+            ds_mbar_expect_tx(&sh.full[cw], DS_UNIT_BYTES);
+            ds_bulk_load(ring + (size_t)cw * DS_UNIT_BYTES, rf.base + (size_t)rf.u * DS_UNIT_BYTES, DS_UNIT_BYTES, &sh.full[cw], evict_first);
+            outstanding = true; req_n = rf_n;
         }
-        return;
-    }
+    };
+    if (lane == 0) { request(); ds_cursor_advance(phases, p.nphases, sh, rf, NS); rf_n += NS; }
 
-    // ---------------------------------------------------------------- consumers
-    const int tid_c = tid - 32, cw = warp - 1;
     const int g = lane >> 2, t = lane & 3;
     const unsigned long long seq = sh.seq;
-    int slot = 0;
-    uint32_t wrap = 0;
-    unsigned segcount = 0;
-    int barrier_idx = 0;
+    if (cta == 0) {
+        // the embedding row of the step's token becomes the residual stream (tag of "phase -1"): the first o_proj adds to it
+        int id = p.rows[0];
+        if (id < 0 || id >= p.vocab) id = 0;             // reported by the staging of layer 0
+        const uint32_t tag0 = ds_tag(seq, p.nphases, -1);
+        for (int k = tid_c; k < p.H; k += DS_THREADS) ds_st_tagged(p.xres + k, __ldg(p.embed + (size_t)id * p.H + k), tag0);
+    }
+    int nbase = 0;                        // units of this CTA consumed in earlier phases
+    const long long ct0 = clock64();
+    long long c_full = 0, c_stage = 0, c_attn = 0, c_seg = 0;
+    long long k_stage[6] = {0, 0, 0, 0, 0, 0}, k_loop[6] = {0, 0, 0, 0, 0, 0};
     for (int ph = 0; ph < p.nphases; ph++) {
-        const DsPhase P = p.phases[ph];
+        const DsPhase P = phases[ph];
         if (P.kind == DS_ATTN) {
-            ds_attention(p, P.layer, sh, tid_c, cta, ncta, s_abort);
-        } else {
-            const float rs = ds_stage_x(p, P, sh, xpl, xsc, tid_c, cta);
-            const int S = P.S;
-            const long long units = (long long)P.groups * S;
-            const long long u0 = units * cta / ncta, u1 = units * (cta + 1) / ncta;
-            const unsigned long long epoch = seq * (unsigned long long)(p.nphases + 1) + (unsigned long long)ph + 1ull;
-            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-            long long seg_start = u0;
-            long long grp = u0 / S;
-            int s = (int)(u0 - grp * S);
-            for (long long u = u0; u < u1; u++) {
-                ds_mbar_wait(&sh.full[slot], wrap & 1u, p, s_abort);
-                const unsigned char* st = ring + (size_t)slot * DS_UNIT_BYTES;
-                const int kb0 = s * DS_UNIT_BLOCKS + 2 * cw;                     // this warp's two blocks of the slice
-                const uint32_t d_lo = *reinterpret_cast<const uint32_t*>(st + 8192 + g * 32 + cw * 4);
-                const uint32_t d_hi = *reinterpret_cast<const uint32_t*>(st + 8192 + (g + 8) * 32 + cw * 4);
-                const float2 xs2 = *reinterpret_cast<const float2*>(xsc + kb0);
-                const float2 dl = __half22float2(*reinterpret_cast<const __half2*>(&d_lo));
-                const float2 dh = __half22float2(*reinterpret_cast<const __half2*>(&d_hi));
-#pragma unroll
-                for (int jj = 0; jj < 2; jj++) {
-                    const int4 a = *reinterpret_cast<const int4*>(st + (size_t)(2 * cw + jj) * 512 + lane * 16);
-                    // columns 0..2 of B are the three planes of x; the other columns are zero (select, so the warp stays converged)
-                    int2 b = *reinterpret_cast<const int2*>(xpl + (size_t)(kb0 + jj) * 96 + min(g, 2) * 32 + t * 8);
-                    b.x = g < 3 ? b.x : 0; b.y = g < 3 ? b.y : 0;
-                    int d0, d1, d2, d3;
-                    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                                 : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-                                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(0));
-                    const float xs = jj ? xs2.y : xs2.x;
-                    const float sl = (jj ? dl.y : dl.x) * xs, shi = (jj ? dh.y : dh.x) * xs;
-                    acc0 = fmaf((float)d0, sl, acc0);
-                    acc1 = fmaf((float)d1, sl, acc1);
-                    acc2 = fmaf((float)d2, shi, acc2);
-                    acc3 = fmaf((float)d3, shi, acc3);
-                }
-                __syncwarp();
-                if (lane == 0) ds_mbar_arrive(&sh.empty[slot]);
-                if (++slot == NS) { slot = 0; wrap++; }
-
-                const bool group_end = (s == S - 1);
-                if (group_end || u == u1 - 1) {
-                    // ---- end of this CTA's segment of the group: sum the warps' partial sums in a fixed order
-                    const unsigned par = segcount & 1u;
-                    sh.red[par][cw][lane] = make_float4(acc0, acc1, acc2, acc3);
-                    ds_named_sync();
-                    if (cw == (int)(segcount % DS_CONSUMER_WARPS)) {
-                        float4 v = sh.red[par][0][lane];
-#pragma unroll
-                        for (int w = 1; w < DS_CONSUMER_WARPS; w++) {
-                            const float4 o = sh.red[par][w][lane];
-                            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                        }
-                        // lane t=0 of a row pair holds planes 0 and 1 (columns 0, 1), lane t=1 plane 2 (column 2)
-                        const float p2_lo = __shfl_down_sync(0xffffffffu, v.x, 1), p2_hi = __shfl_down_sync(0xffffffffu, v.z, 1);
-                        float r_lo = fmaf(v.x, 65536.f, fmaf(v.y, 256.f, p2_lo));
-                        float r_hi = fmaf(v.z, 65536.f, fmaf(v.w, 256.f, p2_hi));
-                        const bool has_head = (seg_start == grp * S);
-                        if (!has_head) {
-                            // a later slice range of a group that starts in an earlier CTA: publish the partial sums
-                            if (t == 0) { p.part[(size_t)cta * 32 + g] = r_lo; p.part[(size_t)cta * 32 + g + 8] = r_hi; }
-                            __syncwarp();
-                            if (lane == 0) { __threadfence(); ds_st_release(p.ctr + 8 + cta, epoch); }
-                        } else {
-                            if (!group_end) {
-                                // the group continues in later CTAs: add their partial sums in CTA order
-                                const long long gend = (grp + 1) * S;
-                                for (int c2 = cta + 1; c2 < ncta; c2++) {
-                                    const long long r0 = units * c2 / ncta, r1 = units * (c2 + 1) / ncta;
-                                    if (r0 >= gend) break;
-                                    if (r1 <= r0) continue;
-                                    if (lane == 0) ds_wait_ge(p.ctr + 8 + c2, epoch, p, s_abort);
-                                    __syncwarp();
-                                    if (t == 0) { r_lo += __ldcg(p.part + (size_t)c2 * 32 + g); r_hi += __ldcg(p.part + (size_t)c2 * 32 + g + 8); }
-                                }
-                            }
-                            if (t == 0) {
-                                const long long row = grp * DS_UNIT_ROWS + g;
-                                if (P.kind == DS_QKV) { p.qkv[row] = r_lo * rs; p.qkv[row + 8] = r_hi * rs; }
-                                else if (P.kind == DS_HEAD) { p.logits[row] = r_lo * rs; p.logits[row + 8] = r_hi * rs; }
-                                else if (P.kind == DS_GATEUP) {
-                                    const float gate = r_lo * rs, upv = r_hi * rs;         // rows 0-7 of a group are gate rows, 8-15 the up rows
-                                    p.mid[grp * 8 + g] = upv * (gate * (1.f / (1.f + __expf(-gate))));
-                                } else {                                                  // o_proj / down: residual add in place
-                                    p.xres[row] = __ldcg(p.xres + row) + r_lo;
-                                    p.xres[row + 8] = __ldcg(p.xres + row + 8) + r_hi;
-                                }
-                            }
-                        }
-                    }
-                    segcount++;
-                    acc0 = acc1 = acc2 = acc3 = 0.f;
-                    seg_start = u + 1;
-                }
-                if (group_end) { s = 0; grp++; } else s++;
+            const long long a0 = clock64();
+            ds_attention(p, P.layer, ph, seq, sh, tid_c, cta, ncta, s_abort);
+            c_attn += clock64() - a0;
+            k_loop[DS_ATTN] += clock64() - a0;
+            continue;
+        }
+        const int S = P.S, units = P.groups * S;
+        const int u0 = sh.range[ph].x, u1 = sh.range[ph].y;
+        if (u1 <= u0) continue;                   // nothing of this matrix here: its x is not needed either
+        const long long s0 = clock64();
+        const uint32_t tag = ds_tag(seq, p.nphases, ph);
+        long long* tl = (p.prof && P.layer == p.prof_layer && tid_c == 0) ? p.prof + (size_t)ncta * 32 + (size_t)cta * 64 + P.kind * 8 : nullptr;
+        if (tl) tl[0] = (long long)blum_globaltimer();
+        ds_sync();                          // the previous phase's warps are done with x and the reduction scratch
+        if (tl) tl[1] = (long long)blum_globaltimer();
+        // groups whose first slice this CTA holds finish here: [gh0, gh1); for o_proj / down their residual rows (written
+        // by the previous residual add, or the embedding row) are fetched together with x
+        const int gh0 = (u0 + S - 1) / S, gh1 = (u1 + S - 1) / S;
+        if (P.kind == DS_O || P.kind == DS_DOWN) {
+            const uint32_t rtag = ds_tag(seq, p.nphases, P.kind == DS_O ? ph - 3 : ph - 2);
+            const int nres = min((gh1 - gh0) * DS_UNIT_ROWS, DS_RESIDUAL_ROWS);
+            for (int i = tid_c; i < nres; i += DS_THREADS) sh.resid[i] = ds_wait_value(p.xres + (size_t)gh0 * DS_UNIT_ROWS + i, rtag, p, s_abort, 2);
+        }
+        // The ring is full and stays so while x is waited for and staged.  So that HBM does not idle meanwhile, every warp
+        // pulls the next units of its stage into L2 (a bounded distance ahead: more of it fills the queues that the
+        // activation words have to pass through); the requests that follow the stall then hit L2.
+        if (lane == 0) {
+            DsCursor pc = rf;
+            int pn = rf_n;
+            for (int d = 0; d < DS_PREFETCH_UNITS && pc.base; d++) {
+                if (pn > pf_n) { ds_bulk_prefetch(pc.base + (size_t)pc.u * DS_UNIT_BYTES, DS_UNIT_BYTES); pf_n = pn; }
+                ds_cursor_advance(phases, p.nphases, sh, pc, NS);
+                pn += NS;
             }
         }
-        if (ph + 1 < p.nphases) {
-            barrier_idx++;
-            ds_grid_sync(p, (seq * (unsigned long long)p.nbarriers + (unsigned long long)barrier_idx) * (unsigned long long)ncta, tid_c, s_abort);
+        if (tid_c == 0) sh.pp_state = 0;
+        if (tl) tl[2] = (long long)blum_globaltimer();
+        const float rs = ds_stage_x(p, P, ph, seq, sh, xpl, xsc, tid_c, s_abort);
+        if (tl) tl[3] = (long long)blum_globaltimer();
+        if (ph + 1 < p.nphases) {                 // the norm weight of the phase after this one: towards L2, out of the way
+            const DsPhase N = phases[ph + 1 + (phases[ph + 1].kind == DS_ATTN ? 1 : 0)];
+            if (N.norm_w) for (int k = tid_c * 32; k < N.K; k += DS_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(N.norm_w + k));
         }
+        c_stage += clock64() - s0;
+        k_stage[P.kind] += clock64() - s0;
+        const long long l0 = clock64();
+        // the last group of the range continues in later CTAs if the range ends inside it
+        const bool split_tail = (u1 % S != 0) && ((u1 / S) * S >= u0);
+        const int first = (cw - nbase % NS + NS) % NS;
+        for (int u = u0 + first; u < u1; u += NS) {
+            const int n = nbase + (u - u0);
+            const uint32_t par = (uint32_t)((n / NS) & 1);
+            const int grp = u / S;
+            const int s = u - grp * S;
+            // The partial sums the later CTAs publish for this CTA's last group are fetched while the stream is still
+            // running (one warp looks once per unit until they are there), so that finishing the group does not start a
+            // chain of round trips at the very end of the phase.
+            if (split_tail && cw == NS - 1 && !sh.pp_state) {
+                float sum;
+                if (ds_fetch_partners(p, units, (u1 / S + 1) * S, cta, ncta, tag, lane, false, s_abort, sum)) {
+                    if (lane < 16) sh.pp_sum[lane] = sum;
+                    __syncwarp();
+                    if (lane == 0) { __threadfence_block(); sh.pp_state = 1; }
+                }
+            }
+            const long long f0 = clock64();
+            ds_mbar_wait(&sh.full[cw], par, p, s_abort, 1, n);
+            c_full += clock64() - f0;
+            const unsigned char* st = ring + (size_t)cw * DS_UNIT_BYTES;
+            // block scales of this lane's two rows and the scales of x for the slice's 16 blocks
+            uint32_t dlo[8], dhi[8];
+            {
+                const uint4 a0 = *reinterpret_cast<const uint4*>(st + 8192 + g * 32), a1 = *reinterpret_cast<const uint4*>(st + 8192 + g * 32 + 16);
+                const uint4 b0 = *reinterpret_cast<const uint4*>(st + 8192 + (g + 8) * 32), b1 = *reinterpret_cast<const uint4*>(st + 8192 + (g + 8) * 32 + 16);
+                dlo[0] = a0.x; dlo[1] = a0.y; dlo[2] = a0.z; dlo[3] = a0.w; dlo[4] = a1.x; dlo[5] = a1.y; dlo[6] = a1.z; dlo[7] = a1.w;
+                dhi[0] = b0.x; dhi[1] = b0.y; dhi[2] = b0.z; dhi[3] = b0.w; dhi[4] = b1.x; dhi[5] = b1.y; dhi[6] = b1.z; dhi[7] = b1.w;
+            }
+            const int kb0 = s * DS_UNIT_BLOCKS;
+            const unsigned char* xb = xpl + (size_t)kb0 * 96 + min(g, 2) * 32 + t * 8;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+#pragma unroll
+            for (int j = 0; j < DS_UNIT_BLOCKS; j++) {
+                const int4 a = *reinterpret_cast<const int4*>(st + j * 512 + lane * 16);
+                // columns 0..2 of B are the three planes of x; the other columns are zero (select, so the warp stays converged)
+                int2 b = *reinterpret_cast<const int2*>(xb + j * 96);
+                b.x = g < 3 ? b.x : 0; b.y = g < 3 ? b.y : 0;
+                int d0, d1, d2, d3;
+                asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                             : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+                             : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(0));
+                const float xs = xsc[kb0 + j];
+                const float2 dl = __half22float2(*reinterpret_cast<const __half2*>(&dlo[j >> 1]));
+                const float2 dh = __half22float2(*reinterpret_cast<const __half2*>(&dhi[j >> 1]));
+                const float sl = ((j & 1) ? dl.y : dl.x) * xs, shi = ((j & 1) ? dh.y : dh.x) * xs;
+                acc0 = fmaf((float)d0, sl, acc0);
+                acc1 = fmaf((float)d1, sl, acc1);
+                acc2 = fmaf((float)d2, shi, acc2);
+                acc3 = fmaf((float)d3, shi, acc3);
+            }
+            __syncwarp();                                           // every lane has read the stage
+            if (lane == 0) { outstanding = false; request(); ds_cursor_advance(phases, p.nphases, sh, rf, NS); rf_n += NS; }
+
+            // ---- the unit's 16 row sums: lane t=0 of a row pair holds planes 0 and 1 (columns 0, 1), lane t=1 plane 2
+            const long long g0c = clock64();
+            const float p2_lo = __shfl_down_sync(0xffffffffu, acc0, 1), p2_hi = __shfl_down_sync(0xffffffffu, acc2, 1);
+            const int pslot = n & (DS_PARTIAL_SLOTS - 1);
+            if (t == 0) {
+                sh.partial[pslot][g] = fmaf(acc0, 65536.f, fmaf(acc1, 256.f, p2_lo));
+                sh.partial[pslot][g + 8] = fmaf(acc2, 65536.f, fmaf(acc3, 256.f, p2_hi));
+            }
+            // the warp that deposits the last unit of the group's segment in this CTA finishes the group
+            const int seg_first = max(u0, grp * S), seg_end = min(u1, (grp + 1) * S);      // units [seg_first, seg_end)
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                const int gi = grp & (DS_PARTIAL_SLOTS - 1);
+                last = (atomicAdd(&sh.gcnt[gi], 1) == (seg_end - seg_first) - 1);
+                if (last) sh.gcnt[gi] = 0;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_block();
+                float v = 0.f;                                               // lane = row of the group (lanes 0..15)
+                if (lane < 16)
+                    for (int uu = seg_first; uu < seg_end; uu++)             // fixed order: reproducible bit for bit
+                        v += sh.partial[(nbase + (uu - u0)) & (DS_PARTIAL_SLOTS - 1)][lane];
+                const bool has_head = (seg_first == grp * S), has_tail = (seg_end == (grp + 1) * S);
+                if (!has_head) {
+                    // a later slice range of a group that starts in an earlier CTA: publish the partial sums
+                    if (lane < 16) ds_st_tagged(p.part + (size_t)cta * 16 + lane, v, tag);
+                } else {
+                    if (!has_tail) {
+                        // the group continues in later CTAs: their partial sums, summed in CTA order, are added as one term
+                        float sum;
+                        if (*reinterpret_cast<volatile int*>(&sh.pp_state)) { __threadfence_block(); sum = lane < 16 ? sh.pp_sum[lane] : 0.f; }
+                        else ds_fetch_partners(p, units, (grp + 1) * S, cta, ncta, tag, lane, true, s_abort, sum);
+                        v += sum;
+                    }
+                    const int row = grp * DS_UNIT_ROWS + lane;
+                    if (P.kind == DS_GATEUP) {
+                        const float upv = __shfl_down_sync(0xffffffffu, v, 8) * rs;         // rows 0-7 of a group are gate rows, 8-15 the up rows
+                        const float gate = v * rs;
+                        if (lane < 8) ds_st_tagged(p.mid + grp * 8 + lane, upv * (gate * (1.f / (1.f + __expf(-gate)))), tag);
+                    } else if (lane < 16) {
+                        if (P.kind == DS_QKV) ds_st_tagged(p.qkv + row, v * rs, tag);
+                        else if (P.kind == DS_HEAD) p.logits[row] = v * rs;
+                        else {                                                              // o_proj / down: residual add in place
+                            const int ri = row - gh0 * DS_UNIT_ROWS;
+                            const uint32_t rtag = ds_tag(seq, p.nphases, P.kind == DS_O ? ph - 3 : ph - 2);
+                            const float base = (ri >= 0 && ri < DS_RESIDUAL_ROWS) ? sh.resid[ri] : ds_wait_value(p.xres + row, rtag, p, s_abort, 2);
+                            ds_st_tagged(p.xres + row, base + v, tag);
+                        }
+                    }
+                }
+            }
+            c_seg += clock64() - g0c;
+        }
+        nbase += u1 - u0;
+        k_loop[P.kind] += clock64() - l0;
+        if (tl) tl[4] = (long long)blum_globaltimer();
     }
+    // a copy this warp requested and never consumed (only after an abort) has to land before the CTA's shared memory goes away
+    if (lane == 0 && outstanding) {
+        const unsigned long long t0 = blum_globaltimer();
+        while (!ds_mbar_try(&sh.full[cw], (uint32_t)((req_n / NS) & 1)) && blum_globaltimer() - t0 < DS_TIMEOUT_NS) {}
+    }
+    if (p.prof && tid_c == 0) {
+        long long* o = p.prof + cta * 32;
+        for (int k = 0; k < 6; k++) { o[8 + 3 * k] = k_stage[k]; o[9 + 3 * k] = k_loop[k]; o[10 + 3 * k] = 0; }
+        o[0] = clock64() - ct0; o[1] = c_full; o[2] = 0; o[3] = c_stage; o[4] = c_attn; o[5] = c_seg; o[6] = 0; o[7] = 0;
+    }
+    // the launch number makes the next launch's tags new; whoever reads it has started, and nobody can finish before everybody
+    // who has work has started (they all feed the last phase)
     if (cta == 0 && tid_c == 0 && !*s_abort) *reinterpret_cast<volatile unsigned long long*>(p.ctr + 1) = seq + 1ull;
 }
 
@@ -564,13 +758,13 @@ int blum_ds_pack(blum_ctx* ctx, const blum_q8_weight* w, const blum_q8_weight* w
     return BLUM_OK;
 }
 
-size_t blum_ds_smem_bytes(int nstages, int kmax) { return (size_t)nstages * DS_UNIT_BYTES + (size_t)kmax * 3 + (size_t)kmax / 32 * 4 + 128; }
+size_t blum_ds_smem_bytes(int kmax) { return (size_t)DS_STAGES * DS_UNIT_BYTES + (size_t)kmax * 3 + (size_t)kmax / 32 * 4 + DS_MAX_PHASES * sizeof(DsPhase) + 128; }
 
 int blum_ds_launch(blum_ctx* ctx, const DsParams& p) {
     static bool attr_set[64] = {};
-    const size_t smem = blum_ds_smem_bytes(p.nstages, p.kmax);
+    const size_t smem = blum_ds_smem_bytes(p.kmax);
     if (ctx->device >= 0 && ctx->device < 64 && !attr_set[ctx->device]) {
-        BLUM_CUDA(ctx, cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - 20 * 1024)));
+        BLUM_CUDA(ctx, cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - 24 * 1024)));
         attr_set[ctx->device] = true;
     }
     void* args[] = {(void*)&p};

@@ -11,11 +11,15 @@
 #define DS_UNIT_K 512
 #define DS_UNIT_BLOCKS 16
 #define DS_UNIT_BYTES 8704
-#define DS_CONSUMER_WARPS 8
-#define DS_CONSUMER_THREADS (32 * DS_CONSUMER_WARPS)
-#define DS_THREADS (32 + DS_CONSUMER_THREADS)      // warp 0 streams weights, warps 1..8 compute
-#define DS_MAX_STAGES 24
+#define DS_WARPS 16
+#define DS_THREADS (32 * DS_WARPS)
+#define DS_STAGES DS_WARPS                          // one ring stage per warp
+#define DS_MAX_PHASES 448                           // 5 per layer + the head: up to 89 layers
 #define DS_ATTN_TILE 256
+#define DS_ATTN_PARTS (DS_THREADS / 128)   // partitions of a tile's positions in the P V product
+#define DS_PARTIAL_SLOTS 128                        // per-unit row sums in flight (power of two; > ring stages + 2 * warps + slices per group)
+#define DS_RESIDUAL_ROWS 512                        // residual rows a CTA keeps in shared memory per phase
+#define DS_PREFETCH_UNITS 2                         // units per warp pulled into L2 at the start of a phase
 
 enum { DS_QKV = 0, DS_ATTN = 1, DS_O = 2, DS_GATEUP = 3, DS_DOWN = 4, DS_HEAD = 5 };
 
@@ -25,28 +29,33 @@ struct DsPhase {
     int kind, layer;
     int K, S;                    // reduction length and its number of 512-wide slices
     int groups;                  // 16-row groups of the (virtual) matrix
-    int pad;
+    int whole;                   // 1: CTAs get whole groups (no group is cut between CTAs)
 };
 
 struct DsParams {
     const DsPhase* phases;
-    int nphases, nbarriers;      // grid barriers per launch (one after every phase but the last)
+    int nphases;
     KvView kv;
     int max_seqs, max_rows;
     const int32_t* rows;         // ids | seq | pos | ctx, each [max_rows]; row 0 is the token of this step
     const float* embed;          // f32 [vocab][H]
-    float *xres, *qkv, *attn, *mid, *logits;
-    float* part;                 // [grid][32]: partial sums of a 16-row group that is split between CTAs
-    float* attn_part;            // [nq][nsplit][130]: split attention partials (o[128], max, sum)
-    unsigned long long* ctr;     // [0] grid-barrier arrivals, [1] launches completed, [2] abort; [8 + cta] split-group flags
+    // activations that cross CTAs: 64-bit words {f32 value, tag of the launch and phase that wrote it}
+    unsigned long long *xres, *qkv, *attn, *mid;
+    unsigned long long* done;        // [grid]: hint words, the tag of the last phase a CTA has finished
+    unsigned long long* part;        // [grid][16]: partial sums of a 16-row group that is split between CTAs
+    unsigned long long* attn_part;   // [nq][nsplit][130]: split attention partials (o[128], max, sum)
+    float* logits;
+    unsigned long long* ctr;     // [1] launches completed, [2] abort, [3..6] where the first wait gave up
     int H, nq, nkv, ffn, vocab;
-    int nsplit, nstages, kmax;
+    int nsplit, kmax;
     float eps, scale;
     RopeFreqs freqs;
     int* err;
+    long long* prof;             // development aid: per-CTA cycle counters [grid][32] + one layer's timeline [grid][64], or null
+    int prof_layer;
 };
 
-size_t blum_ds_smem_bytes(int nstages, int kmax);
+size_t blum_ds_smem_bytes(int kmax);
 int blum_ds_pack(blum_ctx* ctx, const blum_q8_weight* w, const blum_q8_weight* w_up, unsigned char* out);
 size_t blum_ds_packed_bytes(int64_t rows_total, int64_t K);
 int blum_ds_launch(blum_ctx* ctx, const DsParams& p);

@@ -36,11 +36,13 @@ struct StreamPlan {
     uint64_t weights_version = 0;          // version of the model's weights the packed copy was made from
     unsigned char* packed = nullptr;
     DsPhase* d_phases = nullptr;
-    int nphases = 0, nstages = 0, kmax = 0, grid = 0;
-    float* part = nullptr;
-    float* attn_part = nullptr;
+    int nphases = 0, kmax = 0, grid = 0;
+    unsigned long long* words = nullptr;   // tagged activation words: xres | qkv | attn | mid | part | attn_part
+    size_t words_bytes = 0;
+    unsigned long long *xres = nullptr, *qkv = nullptr, *attn = nullptr, *mid = nullptr, *part = nullptr, *attn_part = nullptr, *done = nullptr;
     unsigned long long* ctr = nullptr;
     size_t ctr_bytes = 0;
+    long long* prof = nullptr;             // development aid (blum_llama_stream_profile)
 };
 #define DS_MAX_SPLITS 16
 
@@ -238,16 +240,15 @@ static bool stream_supported(blum_ctx* ctx, blum_llama* m) {
     const blum_llama_cfg& c = m->cfg;
     const int d = c.head_dim, H = c.hidden, qd = m->nq * d;
     bool ok = c.tp_size == 1 && c.act_dtype == BLUM_F32 && c.kv_dtype == BLUM_F32 && d == 128 && !c.embed_q8;
-    ok = ok && H % DS_UNIT_K == 0 && qd % DS_UNIT_K == 0 && m->ffn % DS_UNIT_K == 0;
+    ok = ok && H % DS_UNIT_K == 0 && qd % DS_UNIT_K == 0 && m->ffn % DS_UNIT_K == 0 && 5 * c.layers + 1 <= DS_MAX_PHASES;
     ok = ok && ((m->nq + 2 * m->nkv) * d) % DS_UNIT_ROWS == 0 && H % DS_UNIT_ROWS == 0 && m->ffn % 8 == 0 && m->vocab % DS_UNIT_ROWS == 0;
     int coop = 0;
     if (ok) ok = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device) == cudaSuccess && coop != 0;
     if (ok) {
         const int kmax = std::max(H, std::max(qd, m->ffn));
-        const long long ring = (long long)ctx->smem_optin - 20 * 1024 - (long long)blum_ds_smem_bytes(0, kmax);
-        const int nstages = (int)std::min<long long>(DS_MAX_STAGES, ring / DS_UNIT_BYTES);
-        ok = nstages >= 4;
-        m->sp.kmax = kmax; m->sp.nstages = nstages; m->sp.grid = ctx->sm_count;
+        // ring (one stage per warp) + x as three byte planes + its block scales, beside ~22 KB of static shared memory
+        ok = blum_ds_smem_bytes(kmax) + 24 * 1024 <= ctx->smem_optin;
+        m->sp.kmax = kmax; m->sp.grid = ctx->sm_count;
     }
     m->stream_state = ok ? 1 : 0;
     return ok;
@@ -255,9 +256,10 @@ static bool stream_supported(blum_ctx* ctx, blum_llama* m) {
 
 static void free_stream_plan(blum_llama* m) {
     StreamPlan& sp = m->sp;
-    void* bufs[] = {sp.packed, sp.d_phases, sp.part, sp.attn_part, sp.ctr};
+    void* bufs[] = {sp.packed, sp.d_phases, sp.words, sp.ctr, sp.prof};
+    sp.prof = nullptr; sp.words = nullptr;
     for (void* b : bufs) if (b) cudaFree(b);
-    sp.packed = nullptr; sp.d_phases = nullptr; sp.part = nullptr; sp.attn_part = nullptr; sp.ctr = nullptr;
+    sp.packed = nullptr; sp.d_phases = nullptr; sp.ctr = nullptr;
     sp.built = false;
 }
 
@@ -273,9 +275,15 @@ static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
     if (!sp.packed) {
         cudaError_t e = cudaMalloc((void**)&sp.packed, total);
         if (e == cudaSuccess) e = cudaMalloc((void**)&sp.d_phases, sizeof(DsPhase) * (size_t)(5 * L + 1));
-        if (e == cudaSuccess) e = cudaMalloc((void**)&sp.part, (size_t)sp.grid * 32 * sizeof(float));
-        if (e == cudaSuccess) e = cudaMalloc((void**)&sp.attn_part, (size_t)m->nq * DS_MAX_SPLITS * 130 * sizeof(float));
-        sp.ctr_bytes = (size_t)(8 + sp.grid) * sizeof(unsigned long long);
+        const size_t n_x = (size_t)H, n_qkv = (size_t)qkv_rows, n_attn = (size_t)qd, n_mid = (size_t)m->ffn, n_part = (size_t)sp.grid * 16,
+                     n_ap = (size_t)m->nq * DS_MAX_SPLITS * 130;
+        sp.words_bytes = (n_x + n_qkv + n_attn + n_mid + n_part + n_ap + (size_t)sp.grid) * sizeof(unsigned long long);
+        if (e == cudaSuccess) e = cudaMalloc((void**)&sp.words, sp.words_bytes);
+        if (e == cudaSuccess) {
+            sp.xres = sp.words; sp.qkv = sp.xres + n_x; sp.attn = sp.qkv + n_qkv; sp.mid = sp.attn + n_attn; sp.part = sp.mid + n_mid;
+            sp.attn_part = sp.part + n_part; sp.done = sp.attn_part + n_ap;
+        }
+        sp.ctr_bytes = 8 * sizeof(unsigned long long);
         if (e == cudaSuccess) e = cudaMalloc((void**)&sp.ctr, sp.ctr_bytes);
         if (e != cudaSuccess) {
             free_stream_plan(m);
@@ -283,6 +291,7 @@ static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
         }
     }
     BLUM_CUDA(ctx, cudaMemsetAsync(sp.ctr, 0, sp.ctr_bytes, ctx->stream));
+    BLUM_CUDA(ctx, cudaMemsetAsync(sp.words, 0, sp.words_bytes, ctx->stream));     // tag 0 is never a valid tag
     std::vector<DsPhase> ph;
     unsigned char* at = sp.packed;
     auto add = [&](int kind, int layer, const blum_q8_weight* w, const blum_q8_weight* w_up, const float* norm_w, size_t bytes) -> int {
@@ -291,6 +300,8 @@ static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
         if (w) {
             TRY(blum_ds_pack(ctx, w, w_up, at));
             P.w = at; P.K = (int)w->K; P.S = (int)(w->K / DS_UNIT_K); P.groups = (int)((w_up ? 2 * w->N : w->N) / DS_UNIT_ROWS);
+            // a phase whose whole share fits the ring is short: whole groups per CTA
+            P.whole = ((int64_t)P.groups * P.S <= (int64_t)2 * DS_STAGES * sp.grid) ? 1 : 0;
             at += bytes;
         }
         ph.push_back(P);
@@ -318,18 +329,20 @@ static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
     if (!sp.built || sp.weights_version != m->weights_version) TRY(build_stream_plan(ctx, m));
     const blum_llama_cfg& c = m->cfg;
     DsParams p = {};
-    p.phases = sp.d_phases; p.nphases = sp.nphases; p.nbarriers = sp.nphases - 1;
+    p.phases = sp.d_phases; p.nphases = sp.nphases;
     p.kv = kv_view(m->kv); p.max_seqs = m->kv->max_seqs; p.max_rows = m->max_rows;
     p.rows = m->d_rows; p.embed = m->embed_f32;
-    p.xres = (float*)m->x; p.qkv = (float*)m->qkv; p.attn = (float*)m->attn; p.mid = (float*)m->mid; p.logits = m->logits;
-    p.part = sp.part; p.attn_part = sp.attn_part; p.ctr = sp.ctr;
+    p.xres = sp.xres; p.qkv = sp.qkv; p.attn = sp.attn; p.mid = sp.mid; p.logits = m->logits;
+    p.part = sp.part; p.attn_part = sp.attn_part; p.done = sp.done; p.ctr = sp.ctr;
     p.H = c.hidden; p.nq = m->nq; p.nkv = m->nkv; p.ffn = m->ffn; p.vocab = m->vocab;
     // enough (head, split) items to occupy the grid once contexts are long; one split per 256 cached positions at most
     int nsplit = (int)std::min<int64_t>(DS_MAX_SPLITS, std::max<int64_t>(1, max_ctx_len / 256));
-    p.nsplit = nsplit; p.nstages = sp.nstages; p.kmax = sp.kmax;
+    p.nsplit = nsplit; p.kmax = sp.kmax;
     p.eps = c.rms_eps; p.scale = 1.0f / sqrtf((float)c.head_dim);
     blum_rope_freqs(c.rope_theta, c.head_dim, &p.freqs);
     p.err = ctx->dev_error;
+    p.prof = sp.prof;
+    p.prof_layer = 3;
     TRY(blum_ds_launch(ctx, p));
     return blum_argmax(ctx, m->logits, BLUM_F32, 1, m->vocab, m->d_next);
 }
@@ -532,6 +545,31 @@ int blum_llama_decode_path(blum_ctx* ctx, blum_llama* m) {
     if (!ctx || !m) return BLUM_ERR_INVALID;
     return (m->decode_path != 1 && stream_supported(ctx, m)) ? 2 : 1;
 }
+// Development aid: cycle counters of the last persistent-kernel launch, averaged over CTAs: [0] consumer total, [1] waiting
+// for weight stages, [2] grid barriers, [3] staging x, [4] attention, [5] group reductions, [6] producer waiting for a free
+// stage, [7] producer total, [8 + 3 k + {0, 1, 2}] staging / unit loop / following barrier of phase kind k.  The first call
+// switches the counters on (they are filled by the launches that follow).
+int blum_llama_stream_profile(blum_ctx* ctx, blum_llama* m, double* out, int per_cta) {
+    if (!ctx || !m || !out) return BLUM_ERR_INVALID;
+    StreamPlan& sp = m->sp;
+    if (!stream_supported(ctx, m)) return blum_fail(ctx, BLUM_ERR_STATE, "stream profile: the model does not use the persistent kernel");
+    const size_t n = (size_t)sp.grid * 96;
+    if (!sp.prof) {
+        BLUM_CUDA(ctx, cudaMalloc((void**)&sp.prof, n * sizeof(long long)));
+        BLUM_CUDA(ctx, cudaMemsetAsync(sp.prof, 0, n * sizeof(long long), ctx->stream));
+    }
+    std::vector<long long> h(n);
+    BLUM_CUDA(ctx, cudaMemcpyAsync(h.data(), sp.prof, n * sizeof(long long), cudaMemcpyDeviceToHost, ctx->stream));
+    BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // out: [32] averages over CTAs, then [32] maxima, then [32] minima; with per_cta also the raw [grid][32] table
+    for (int i = 0; i < 32; i++) {
+        double s = 0, mx = -1e300, mn = 1e300;
+        for (int c = 0; c < sp.grid; c++) { const double v = (double)h[(size_t)c * 32 + i]; s += v; mx = v > mx ? v : mx; mn = v < mn ? v : mn; }
+        out[i] = s / sp.grid; out[32 + i] = mx; out[64 + i] = mn;
+    }
+    if (per_cta) for (size_t i = 0; i < n; i++) out[96 + i] = (double)h[i];      // [grid][32] counters, then [grid][64] timeline of one layer
+    return BLUM_OK;
+}
 int blum_llama_set_comm(blum_ctx* ctx, blum_llama* m, blum_comm* comm) {
     if (!ctx || !m) return BLUM_ERR_INVALID;
     m->comm = comm;
@@ -643,7 +681,18 @@ static int finish_step(blum_ctx* ctx, blum_llama* m, const char* what) {
         const int word = *h_err;
         BLUM_CUDA(ctx, cudaMemsetAsync(ctx->dev_error, 0, sizeof(int), ctx->stream));
         // a stream kernel that gave up leaves its barrier counters mid-way: start the next launch from zero
-        if (m->sp.ctr) BLUM_CUDA(ctx, cudaMemsetAsync(m->sp.ctr, 0, m->sp.ctr_bytes, ctx->stream));
+        unsigned long long where[8] = {};
+        if (m->sp.ctr) {
+            cudaMemcpyAsync(where, m->sp.ctr, sizeof where, cudaMemcpyDeviceToHost, ctx->stream);
+            cudaStreamSynchronize(ctx->stream);
+            // launch numbers start again from zero, so the tags the words still carry would come round again: clear them too
+            BLUM_CUDA(ctx, cudaMemsetAsync(m->sp.ctr, 0, m->sp.ctr_bytes, ctx->stream));
+            BLUM_CUDA(ctx, cudaMemsetAsync(m->sp.words, 0, m->sp.words_bytes, ctx->stream));
+        }
+        if (where[3])
+            return blum_fail(ctx, BLUM_ERR_DEVICE, "%s: device error word = 0x%x; the persistent decode kernel gave up a wait (site %llu: 1 weight "
+                             "stage, 2 activation word, 3 attention input, 4 split-group partial) in CTA %llu, waited for %llu, saw %llu; launch %llu",
+                             what, word, where[3], where[4], where[5], where[6], where[1]);
         return blum_fail(ctx, BLUM_ERR_DEVICE, "%s: device error word = 0x%x (bounded wait expired or bad page / sequence index)", what, word);
     }
     return BLUM_OK;
