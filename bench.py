@@ -342,6 +342,12 @@ def run_secondary(args, rank, world, local_rank):
                 print(json.dumps(out), flush=True)
             dist.barrier()
             dist.destroy_process_group()
+    elif args.workload == "sweep":
+        if rank == 0:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+            ms = [int(v) for v in args.m.split(",")] if args.m else None
+            print(json.dumps(workloads.sweep(ctx, ms=ms, iters=max(args.steps, 5), hbm_peak=float(peaks.get("hbm_gbs", 6650.0)),
+                                             tc_peak=float(peaks.get("bf16_tflops", 1590.0)))), flush=True)
     elif args.workload == "moe":
         if rank == 0:
             print(json.dumps(workloads.moe_layer(ctx, args.steps, args.warmup)), flush=True)
@@ -375,10 +381,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "serve64", "tp70b", "moe", "moe_ep"],
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "serve64", "tp70b", "moe", "moe_ep", "sweep"],
                     help="decode8b (default, the headline metric) or one of the secondary configurations")
     ap.add_argument("--layers", type=int, default=None, help="secondary workloads only: truncate the model to this many layers")
     ap.add_argument("--prompt", type=int, default=None, help="tp70b only: prompt length (default 1024)")
+    ap.add_argument("--m", default=None, help="sweep only: comma-separated row counts (default 1,8,64,512,4096)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -3,7 +3,9 @@
  * inference compiler runs for Q8_0-quantized transformer decoding.
  *
  * Each entry point names the reference interface it stands in for (paths are relative
- * to the luminal source tree).  The convention throughout:
+ * to the luminal source tree), or says that the reference has no counterpart.  Hooks that
+ * exist for tests, benches and development (seeded generators, timers, traces) are declared
+ * in blum_dev.h, not here.  The convention throughout:
  *   - every function returns an int status: 0 = ok, <0 = error (see blum_status);
  *     nothing aborts, traps or throws across this boundary (the reference panics
  *     instead: crates/luminal_cuda/src/quantized.rs:144,163);
@@ -49,14 +51,18 @@ typedef struct blum_comm blum_comm;
 /* Replaces CudaContext::new(0) + default_stream() (crates/luminal_cuda/src/quantized.rs:247,142). */
 int blum_ctx_create(int device, blum_ctx** out);
 int blum_ctx_destroy(blum_ctx* ctx);
-/* Run on a caller-owned cudaStream_t (pass 0 for the legacy default stream) so that ordering
- * with untouched luminal ops on cudarc's stream is kept. */
+/* Run on a caller-owned cudaStream_t (pass 0 for the legacy default stream) so that ordering with untouched luminal
+ * ops is kept: the reference launches everything on `device.default_stream()` (crates/luminal_cuda/src/quantized.rs:142). */
 int blum_ctx_set_stream(blum_ctx* ctx, void* cuda_stream);
 void* blum_ctx_stream(blum_ctx* ctx);
+/* Message of the last failed call on this context.  No counterpart: the reference panics with its message
+ * (crates/luminal_cuda/src/quantized.rs:144,163). */
 const char* blum_last_error(blum_ctx* ctx);
+/* Device ordinal and SM count of the context; the reference has a fixed device 0 (crates/luminal_cuda/src/quantized.rs:247). */
 int blum_ctx_device(blum_ctx* ctx);
 int blum_ctx_sm_count(blum_ctx* ctx);
-/* Library version string and the gencode it was built for. */
+/* Library version string and the gencode it was built for.  No counterpart: the reference compiles its kernels at run time
+ * (crates/luminal_cuda/src/lib.rs:237-258). */
 const char* blum_version(void);
 
 /* ------------------------------------------------------------------ buffers
@@ -83,30 +89,6 @@ int blum_graph_end(blum_ctx* ctx, void** graph_exec_out, int* n_kernels_out);
 int blum_graph_launch(blum_ctx* ctx, void* graph_exec, int n_kernels);
 int blum_graph_destroy(blum_ctx* ctx, void* graph_exec);
 
-/* Development aid: per-launch device timestamps (globaltimer ns) of the kernels that support it (decode GEMV and
- * fused decode attention).  Enable BEFORE the launches are issued or captured; each such launch then takes the next
- * record {earliest CTA start, latest dependency-wait return, latest prologue end, latest CTA end}.  A captured graph
- * keeps writing to the records it was captured with; blum_trace_reset clears them between replays. */
-int blum_trace_enable(blum_ctx* ctx, int max_launches);
-int blum_trace_reset(blum_ctx* ctx);
-int blum_trace_read(blum_ctx* ctx, uint64_t* out, int max_records, int* n_records);
-
-/* Timing on the context's stream (cudaEvent pairs); slot in [0,64). */
-int blum_timer_start(blum_ctx* ctx, int slot);
-int blum_timer_stop(blum_ctx* ctx, int slot);
-int blum_timer_elapsed_ms(blum_ctx* ctx, int slot, float* ms); /* synchronises on the stop event */
-/* Writes `bytes` of a private scratch buffer (> L2) so the next kernel starts cold. */
-int blum_flush_l2(blum_ctx* ctx);
-
-/* ------------------------------------------------------------------ seeded generators
- * Counter-based inputs shared by tests and benches: h = mix64(key(seed,tensor_id) + index).
- * Integer parts run on the device; scales / normals are made on the host in double and
- * uploaded, so host and device agree bit for bit. */
-int blum_gen_q8_quants_host(uint64_t seed, uint64_t tensor_id, int64_t n, int8_t* out);
-int blum_gen_q8_scales_host(uint64_t seed, uint64_t tensor_id, int64_t nblocks, uint16_t* out_f16);
-int blum_gen_normal_host(uint64_t seed, uint64_t tensor_id, int64_t n, float stddev, float* out);
-int blum_gen_token_ids_host(uint64_t seed, uint64_t tensor_id, int64_t n, int32_t vocab, int32_t* out);
-
 /* ------------------------------------------------------------------ Q8_0 weights
  * A Q8_0 tensor [N,K] arrives as raw GGUF bytes: 34-byte blocks {f16 d; int8 qs[32]} in
  * row-major block order (crates/luminal_cuda/src/quantized.rs:30-33; uploaded as CudaData<u8>
@@ -116,10 +98,6 @@ int blum_q8_0_weight_from_gguf_bytes(blum_ctx* ctx, const void* dev_bytes, int64
                                      blum_q8_weight** out);
 int blum_q8_0_weight_from_host_gguf_bytes(blum_ctx* ctx, const void* host_bytes, int64_t N, int64_t K,
                                           blum_q8_weight** out);
-/* Generates quants on the device from (seed, tensor_id) and uploads host-made scales
- * (nblocks = N*K/32 f16 values, e.g. from blum_gen_q8_scales_host). */
-int blum_q8_0_weight_generate(blum_ctx* ctx, uint64_t seed, uint64_t tensor_id, int64_t N, int64_t K,
-                              const uint16_t* host_scales_f16, blum_q8_weight** out);
 /* New weight whose rows are the rows of `parts[0..n)` stacked along N (fused q/k/v, gate/up). */
 int blum_q8_0_weight_concat_rows(blum_ctx* ctx, blum_q8_weight* const* parts, int nparts,
                                  blum_q8_weight** out);
@@ -154,16 +132,6 @@ int blum_q8_0_matmul_fused(blum_ctx* ctx, const blum_q8_weight* w, const void* x
 int blum_q8_0_matmul_swiglu(blum_ctx* ctx, const blum_q8_weight* w_gate, const blum_q8_weight* w_up,
                             const void* x, blum_dtype x_dtype, const float* norm_weight, float eps,
                             void* y, blum_dtype y_dtype, int64_t M);
-/* Development hook: run GEMV variant `variant` (see q8_gemv.cu) regardless of the dispatcher. */
-int blum_q8_0_gemv_variant(blum_ctx* ctx, int variant, const blum_q8_weight* w, const void* x,
-                           blum_dtype x_dtype, void* y, blum_dtype y_dtype, int64_t M);
-
-/* Measurement helper: captures `iters` matmul launches (cycling through ws[0..nws) so that consecutive
- * launches read different weights) in one CUDA graph and returns the average device time per launch.
- * variant < 0 uses the dispatcher of blum_q8_0_matmul. */
-int blum_q8_0_matmul_timed(blum_ctx* ctx, blum_q8_weight* const* ws, int nws, const void* x, blum_dtype x_dtype,
-                           void* y, blum_dtype y_dtype, int64_t M, int variant, int iters, float* avg_us);
-
 /* Embedding row dequantisation; replaces QuantizedGather<T>::process
  * (crates/luminal_cuda/src/quantized.rs:202-233).  ids are int32 on the device. */
 int blum_q8_0_gather(blum_ctx* ctx, const blum_q8_weight* w, const int32_t* ids, int64_t T,
@@ -285,8 +253,6 @@ int blum_bf16_matmul(blum_ctx* ctx, const void* w_bf16, int64_t N, int64_t K, co
  * per 32 elements along K. */
 int blum_mxfp4_weight_from_host(blum_ctx* ctx, const void* nibbles, const void* scales, int E, int64_t N, int64_t K,
                                 blum_mxfp4_weight** out);
-int blum_mxfp4_weight_generate(blum_ctx* ctx, uint64_t seed, uint64_t tensor_id, int E, int64_t N, int64_t K,
-                               blum_mxfp4_weight** out);
 int blum_mxfp4_weight_download(blum_ctx* ctx, const blum_mxfp4_weight* w, void* nibbles_out, void* scales_out);
 int blum_mxfp4_weight_free(blum_ctx* ctx, blum_mxfp4_weight* w);
 int blum_moe_route_topk(blum_ctx* ctx, const void* x_bf16, const void* router_w_bf16, const float* router_bias,
@@ -303,18 +269,25 @@ int blum_moe_unpermute(blum_ctx* ctx, const void* yp_bf16, const int32_t* slot_o
 /* ------------------------------------------------------------------ multi-GPU (no counterpart in the reference:
  * luminal hard-codes device 0, crates/luminal_cuda/src/quantized.rs:247)
  * One process per GPU.  Rank 0 calls blum_comm_unique_id and hands the 128 bytes to every rank out of band; each rank
- * then calls blum_comm_init_rank with its own context.  Collectives run on the context's stream (NCCL over NVLink). */
+ * then calls blum_comm_init_rank with its own context.  Collectives run on the context's stream (NCCL over NVLink).
+ * Timeouts: every call that can wait for another rank takes timeout_ms.  For the init, timeout_ms > 0 gives up when a rank
+ * has not joined in time (0 blocks as ncclCommInitRank does).  For a collective, timeout_ms = 0 only enqueues it (it may
+ * then be captured in a CUDA graph); timeout_ms > 0 makes the call return when the collective has finished, and if it has
+ * not finished in time (a peer never arrived) or NCCL reports an asynchronous error, a host watchdog aborts the
+ * communicator - which ends the waiting kernel, so the context and its stream stay usable - and the call returns
+ * BLUM_ERR_COMM.  An aborted communicator fails every later call at once; destroy it and build a new one. */
 int blum_comm_unique_id(void* out_128_bytes);
-int blum_comm_init_rank(blum_ctx* ctx, int nranks, int rank, const void* id_128_bytes, blum_comm** out);
+int blum_comm_init_rank(blum_ctx* ctx, int nranks, int rank, const void* id_128_bytes, int timeout_ms, blum_comm** out);
 int blum_comm_destroy(blum_ctx* ctx, blum_comm* comm);
 int blum_comm_rank(const blum_comm* comm);
 int blum_comm_size(const blum_comm* comm);
 /* In-place sum over ranks (tensor-parallel exchange after the row-parallel o_proj / down_proj). */
-int blum_allreduce_sum(blum_ctx* ctx, blum_comm* comm, void* buf, int64_t count, blum_dtype dtype);
-int blum_allgather(blum_ctx* ctx, blum_comm* comm, const void* send, void* recv, int64_t bytes_per_rank);
+int blum_allreduce_sum(blum_ctx* ctx, blum_comm* comm, void* buf, int64_t count, blum_dtype dtype, int timeout_ms);
+int blum_allgather(blum_ctx* ctx, blum_comm* comm, const void* send, void* recv, int64_t bytes_per_rank, int timeout_ms);
 /* Variable all-to-all in bytes (expert-parallel dispatch / combine); the four arrays are host int64 [size]. */
 int blum_alltoallv(blum_ctx* ctx, blum_comm* comm, const void* send, const int64_t* send_bytes,
-                   const int64_t* send_offsets, void* recv, const int64_t* recv_bytes, const int64_t* recv_offsets);
+                   const int64_t* send_offsets, void* recv, const int64_t* recv_bytes, const int64_t* recv_offsets,
+                   int timeout_ms);
 
 /* ------------------------------------------------------------------ Llama decoder
  * The model of examples/llama/src/model.rs as one object: weights, KV pool, scratch and a
@@ -335,9 +308,6 @@ typedef struct blum_llama_cfg {
 
 int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out);
 int blum_llama_destroy(blum_ctx* ctx, blum_llama* m);
-/* Fills all weights from the seeded generator (Q8_0 linears, N(0,0.02) f32 embedding, norm = 1).
- * tensor ids follow blum_llama_tensor_id(). */
-int blum_llama_generate_weights(blum_ctx* ctx, blum_llama* m, uint64_t seed);
 /* Installs one tensor by GGUF name ("blk.3.attn_q.weight", "token_embd.weight", ...;
  * examples/llama/src/model.rs:250-259) from host bytes: Q8_0 blocks or f32. */
 int blum_llama_set_tensor(blum_ctx* ctx, blum_llama* m, const char* gguf_name, const void* host_bytes,
@@ -364,14 +334,6 @@ int blum_llama_decode_loop(blum_ctx* ctx, blum_llama* m, int seq, int32_t first_
  * kernels.  blum_llama_decode_path returns the path a single-sequence step takes now: 2 = persistent kernel, 1 = graph. */
 int blum_llama_set_decode_path(blum_ctx* ctx, blum_llama* m, int path);
 int blum_llama_decode_path(blum_ctx* ctx, blum_llama* m);
-/* Development aid: average per-CTA cycle counters of the persistent decode kernel (see csrc/llama.cu). */
-int blum_llama_stream_profile(blum_ctx* ctx, blum_llama* m, double* out, int per_cta);
-/* Borrowed handles to the model's own tensors, for per-kernel timing: which = 0 fused q/k/v, 1 attn_output,
- * 2 ffn_gate, 3 ffn_up, 4 ffn_down, 5 output head (layer ignored).  Norm weights: 0 attn_norm, 1 ffn_norm, 2 output_norm. */
-blum_q8_weight* blum_llama_layer_weight(blum_llama* m, int layer, int which);
-const float* blum_llama_norm_weight(blum_llama* m, int layer, int which);
-/* Number of kernels launched by this library on ctx since creation (bench bookkeeping). */
-int64_t blum_launch_count(blum_ctx* ctx);
 /* Bytes of Q8_0 weights read per decoded token (algorithmic). */
 int64_t blum_llama_weight_bytes(const blum_llama* m);
 

@@ -1,4 +1,4 @@
-"""ctypes binding of libblum.so (the C ABI declared in include/blum.h).
+"""ctypes binding of libblum.so (the C ABI declared in include/blum.h, plus the development hooks of include/blum_dev.h).
 
 The library is the product; this module only loads it and declares argument types.
 There is no fallback: if the shared library is missing, importing raises.
@@ -10,6 +10,7 @@ import re
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libblum.so")
 HEADER_PATH = os.path.join(HERE, "..", "include", "blum.h")
+DEV_HEADER_PATH = os.path.join(HERE, "..", "include", "blum_dev.h")
 
 F32, F16, BF16 = 0, 1, 2
 DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2}
@@ -69,13 +70,20 @@ def declared_functions(header_path=HEADER_PATH):
     return protos
 
 
+def all_declared_functions():
+    """The product ABI (blum.h) plus the development hooks (blum_dev.h)."""
+    protos = declared_functions(HEADER_PATH)
+    protos.update(declared_functions(DEV_HEADER_PATH))
+    return protos
+
+
 def load(path=LIB_PATH):
     if not os.path.exists(path):
         raise ImportError(
             "libblum.so not found at %s: build it with `python -m luminal_b200.build` "
             "(there is no CPU fallback)" % path)
     lib = C.CDLL(path)
-    for name, (restype, argtypes) in declared_functions().items():
+    for name, (restype, argtypes) in all_declared_functions().items():
         fn = getattr(lib, name)   # AttributeError if the library lacks a declared symbol
         fn.restype = restype
         fn.argtypes = argtypes

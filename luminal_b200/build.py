@@ -26,6 +26,7 @@ def sources():
 def headers():
     hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     hs.append(os.path.join(HERE, "..", "include", "blum.h"))
+    hs.append(os.path.join(HERE, "..", "include", "blum_dev.h"))
     return hs
 
 

@@ -338,8 +338,7 @@ int blum_attn_prefill_paged(blum_ctx* ctx, blum_kv* kv, int layer, const void* q
     if (T == 0) return BLUM_OK;
     if (seq < 0 || seq >= kv->max_seqs || kv->seq_len[seq] < p + T)
         return blum_fail(ctx, BLUM_ERR_STATE, "attention prefill: sequence %d does not hold %lld tokens", seq, (long long)(p + T));
-    static const bool no_mma = getenv("BLUM_ATTN_NO_MMA") && (atoi(getenv("BLUM_ATTN_NO_MMA")) & 2) != 0;   // measurement aid (bit 1: prompt kernel)
-    if (!no_mma && q_heads > 0 && q_heads % kv->kv_heads == 0 && blum_attn_prefill_mma_covers(dtype, kv->dtype, kv->head_dim, kv->page_size))
+    if (q_heads > 0 && q_heads % kv->kv_heads == 0 && blum_attn_prefill_mma_covers(dtype, kv->dtype, kv->head_dim, kv->page_size))
         return blum_attn_prefill_mma(ctx, kv, layer, q, dtype, q_heads, seq, p, T, out);
     int32_t* rows = nullptr;
     BLUM_CUDA(ctx, cudaMallocAsync((void**)&rows, (size_t)2 * T * sizeof(int32_t), ctx->stream));

@@ -308,9 +308,7 @@ int blum_attn_decode_fused(blum_ctx* ctx, blum_kv* kv, int layer, const void* qk
     p.part_o = (float*)scratch;
     p.part_ml = p.part_o ? p.part_o + (size_t)rows * q_heads * nsplit * kv->head_dim : nullptr;
     const int g = q_heads / kv->kv_heads, d = kv->head_dim;
-    // measurement aid: BLUM_ATTN_NO_MMA=1 keeps 16-bit shapes on the CUDA-core kernel
-    static const bool no_mma = getenv("BLUM_ATTN_NO_MMA") && (atoi(getenv("BLUM_ATTN_NO_MMA")) & 1) != 0;   // (bit 0: decode kernel)
-    if (!no_mma && blum_attn_decode_mma_covers(dtype, kv->dtype, g, d, kv->page_size)) rc = blum_attn_decode_mma_launch(ctx, p, dtype, (int)rows, nsplit, g, d);
+    if (blum_attn_decode_mma_covers(dtype, kv->dtype, g, d, kv->page_size)) rc = blum_attn_decode_mma_launch(ctx, p, dtype, (int)rows, nsplit, g, d);
     else if (dtype == BLUM_F32 && kv->dtype == BLUM_F32) rc = launch_fused_gd<float, float>(ctx, p, (int)rows, nsplit, g, d);
     else if (dtype == BLUM_BF16 && kv->dtype == BLUM_BF16) rc = launch_fused_gd<__nv_bfloat16, __nv_bfloat16>(ctx, p, (int)rows, nsplit, g, d);
     else if (dtype == BLUM_F16 && kv->dtype == BLUM_F16) rc = launch_fused_gd<__half, __half>(ctx, p, (int)rows, nsplit, g, d);

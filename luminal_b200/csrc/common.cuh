@@ -8,6 +8,7 @@
 #include <string>
 #include <vector>
 #include "../../include/blum.h"
+#include "../../include/blum_dev.h"
 
 struct blum_ctx {
     int device = 0;
@@ -181,7 +182,7 @@ int blum_q8_generate_window(blum_ctx* ctx, blum_q8_weight* w, int64_t dst_row0, 
 int blum_q8_fill_from_host_gguf(blum_ctx* ctx, blum_q8_weight* w, int64_t dst_row0, int64_t nrows, const void* host_bytes,
                                 int64_t K_full, int64_t src_row0, int64_t k0);
 int blum_gemv_dispatch(blum_ctx* ctx, const blum_q8_weight* w, const blum_q8_weight* w_up, const void* x, int xdt,
-                       const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M, int variant);
+                       const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M);
 struct blum_kv;
 int blum_attn_rows(blum_ctx* ctx, blum_kv* kv, int layer, const void* q, int dtype, int q_heads, const int32_t* seq_ids,
                    const int32_t* ctx_lens, int64_t rows, int nsplit, void* scratch, void* out);

@@ -106,19 +106,6 @@ static size_t act_bytes(const blum_llama* m, int64_t elems) { return (size_t)ele
 // ------------------------------------------------------------------ forward for R rows
 // rows are described by d_rows (ids, seq, pos, ctx); head_rows = rows whose logits are needed
 // (all for decode, the last one for prefill); everything is enqueued on ctx->stream.
-// measurement aid: BLUM_DEBUG_SYNC=1 waits for the device after every step of the batched path and names the first
-// step after which an error is pending
-static int debug_sync(blum_ctx* ctx, const char* what, int layer) {
-    static const bool on = getenv("BLUM_DEBUG_SYNC") && atoi(getenv("BLUM_DEBUG_SYNC")) != 0;
-    if (!on) return BLUM_OK;
-    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-    cudaStreamIsCapturing(ctx->stream, &st);
-    if (st != cudaStreamCaptureStatusNone) return BLUM_OK;
-    const cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) return blum_fail(ctx, BLUM_ERR_CUDA, "device error after %s of layer %d: %s", what, layer, cudaGetErrorString(e));
-    return BLUM_OK;
-}
-
 static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool last_row_only) {
     const blum_llama_cfg& c = m->cfg;
     const blum_dtype adt = (blum_dtype)c.act_dtype;
@@ -134,32 +121,24 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         PdlGuard(blum_ctx* c_, bool keep) : c(c_), saved(c_->pdl) { if (!keep) c->pdl = false; }
         ~PdlGuard() { c->pdl = saved; }
     } pdl_guard(ctx, fused);
-    // measurement aid: BLUM_DEBUG_SKIP is a bit mask of fused-path launches to leave out (results are then wrong);
-    // 1 qkv, 2 attention, 4 o_proj, 8 gate/up, 16 down, 32 head, 64 argmax
-    const char* skip_env = getenv("BLUM_DEBUG_SKIP");
-    const int skip = skip_env ? atoi(skip_env) : 0;
     for (int l = 0; l < c.layers; l++) {
         const LayerW& w = m->L[l];
         if (fused) {
-            if (!(skip & 1)) TRY(blum_gemv_dispatch(ctx, w.wqkv, nullptr, m->x, adt, w.attn_norm, c.rms_eps, nullptr, m->qkv, adt, R, -1));
+            TRY(blum_gemv_dispatch(ctx, w.wqkv, nullptr, m->x, adt, w.attn_norm, c.rms_eps, nullptr, m->qkv, adt, R));
         } else {
             // (for l > 0 the previous layer's down-projection add already produced xn = rmsnorm(x) with this layer's weight)
             if (l == 0) TRY(blum_rmsnorm(ctx, m->x, nullptr, w.attn_norm, c.rms_eps, m->xn, nullptr, adt, R, H));
             TRY(blum_q8_0_matmul(ctx, w.wqkv, m->xn, adt, m->qkv, adt, R));
-            TRY(debug_sync(ctx, "norm+qkv gemm", l));
         }
         if (!last_row_only) {
             // decode: every row is the next token of its own sequence -> RoPE + append + attention in one launch
-            if (!(skip & 2)) TRY(blum_attn_decode_fused(ctx, m->kv, l, m->qkv, adt, m->nq, c.rope_theta, seq, ctxl, R, nsplit, m->attn_scratch, m->attn));
+            TRY(blum_attn_decode_fused(ctx, m->kv, l, m->qkv, adt, m->nq, c.rope_theta, seq, ctxl, R, nsplit, m->attn_scratch, m->attn));
         } else {
             TRY(blum_rope_kv_append(ctx, m->kv, l, m->qkv, adt, m->nq, c.rope_theta, seq, pos, R, m->q));
-            TRY(debug_sync(ctx, "rope+append", l));
-            static const bool no_mma = getenv("BLUM_ATTN_NO_MMA") && (atoi(getenv("BLUM_ATTN_NO_MMA")) & 2) != 0;   // measurement aid (bit 1: prompt kernel)
-            if (!no_mma && m->pre_seq >= 0 && blum_attn_prefill_mma_covers(adt, m->kv->dtype, d, m->kv->page_size))
+            if (m->pre_seq >= 0 && blum_attn_prefill_mma_covers(adt, m->kv->dtype, d, m->kv->page_size))
                 TRY(blum_attn_prefill_mma(ctx, m->kv, l, m->q, adt, m->nq, m->pre_seq, m->pre_p0, R, m->attn));
             else
                 TRY(blum_attn_rows(ctx, m->kv, l, m->q, adt, m->nq, seq, ctxl, R, nsplit, m->attn_scratch, m->attn));
-            TRY(debug_sync(ctx, "prompt attention", l));
         }
         // row-parallel projections: with tensor parallelism every rank holds a K-slice, the partial products are
         // summed over ranks (NCCL all-reduce) and only then added to the residual stream
@@ -167,37 +146,31 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         if (tp && !m->comm) return blum_fail(ctx, BLUM_ERR_STATE, "llama: tp_size=%d but no communicator was set (blum_llama_set_comm)", c.tp_size);
         if (fused) {
             if (!tp) {
-                if (!(skip & 4)) TRY(blum_gemv_dispatch(ctx, w.wo, nullptr, m->attn, adt, nullptr, 0.f, m->x, m->x, adt, R, -1));
+                TRY(blum_gemv_dispatch(ctx, w.wo, nullptr, m->attn, adt, nullptr, 0.f, m->x, m->x, adt, R));
             } else {
-                TRY(blum_gemv_dispatch(ctx, w.wo, nullptr, m->attn, adt, nullptr, 0.f, nullptr, m->xn, adt, R, -1));
-                TRY(blum_allreduce_sum(ctx, m->comm, m->xn, (int64_t)R * H, adt));
+                TRY(blum_gemv_dispatch(ctx, w.wo, nullptr, m->attn, adt, nullptr, 0.f, nullptr, m->xn, adt, R));
+                TRY(blum_allreduce_sum(ctx, m->comm, m->xn, (int64_t)R * H, adt, 0));
                 TRY(blum_add(ctx, m->x, m->xn, m->x, adt, (int64_t)R * H));
             }
-            if (!(skip & 8)) TRY(blum_gemv_dispatch(ctx, w.wgate, w.wup, m->x, adt, w.ffn_norm, c.rms_eps, nullptr, m->mid, adt, R, -1));
+            TRY(blum_gemv_dispatch(ctx, w.wgate, w.wup, m->x, adt, w.ffn_norm, c.rms_eps, nullptr, m->mid, adt, R));
             if (!tp) {
-                if (!(skip & 16)) TRY(blum_gemv_dispatch(ctx, w.wdown, nullptr, m->mid, adt, nullptr, 0.f, m->x, m->x, adt, R, -1));
+                TRY(blum_gemv_dispatch(ctx, w.wdown, nullptr, m->mid, adt, nullptr, 0.f, m->x, m->x, adt, R));
             } else {
-                TRY(blum_gemv_dispatch(ctx, w.wdown, nullptr, m->mid, adt, nullptr, 0.f, nullptr, m->xn, adt, R, -1));
-                TRY(blum_allreduce_sum(ctx, m->comm, m->xn, (int64_t)R * H, adt));
+                TRY(blum_gemv_dispatch(ctx, w.wdown, nullptr, m->mid, adt, nullptr, 0.f, nullptr, m->xn, adt, R));
+                TRY(blum_allreduce_sum(ctx, m->comm, m->xn, (int64_t)R * H, adt, 0));
                 TRY(blum_add(ctx, m->x, m->xn, m->x, adt, (int64_t)R * H));
             }
         } else {
             // residual add and the following RMSNorm in one kernel: x <- x + proj (rounded as the separate add would),
             // xn <- rmsnorm(x) * weight.  The projection lands in the gate buffer, which is free here.
             TRY(blum_q8_0_matmul(ctx, w.wo, m->attn, adt, m->gate, adt, R));
-            TRY(debug_sync(ctx, "o gemm", l));
-            if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt));
+            if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt, 0));
             TRY(blum_rmsnorm(ctx, m->x, m->gate, w.ffn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
-            TRY(debug_sync(ctx, "add+norm", l));
             TRY(blum_q8_0_matmul(ctx, w.wgate, m->xn, adt, m->gate, adt, R));
-            TRY(debug_sync(ctx, "gate gemm", l));
             TRY(blum_q8_0_matmul(ctx, w.wup, m->xn, adt, m->up, adt, R));
-            TRY(debug_sync(ctx, "up gemm", l));
             TRY(blum_swiglu(ctx, m->gate, m->up, m->mid, adt, (int64_t)R * m->ffn));
-            TRY(debug_sync(ctx, "swiglu", l));
             TRY(blum_q8_0_matmul(ctx, w.wdown, m->mid, adt, m->gate, adt, R));
-            TRY(debug_sync(ctx, "down gemm", l));
-            if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt));
+            if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt, 0));
             if (l + 1 < c.layers) TRY(blum_rmsnorm(ctx, m->x, m->gate, m->L[l + 1].attn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
             else TRY(blum_add(ctx, m->x, m->gate, m->x, adt, (int64_t)R * H));
         }
@@ -207,7 +180,7 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
     const int HR = last_row_only ? 1 : R;
     const char* xh = (const char*)m->x + (last_row_only ? act_bytes(m, (int64_t)(R - 1) * H) : 0);
     if (HR <= GEMV_ROWS) {
-        if (!(skip & 32)) TRY(blum_gemv_dispatch(ctx, m->head, nullptr, xh, adt, m->out_norm, c.rms_eps, nullptr, m->logits, BLUM_F32, HR, -1));
+        TRY(blum_gemv_dispatch(ctx, m->head, nullptr, xh, adt, m->out_norm, c.rms_eps, nullptr, m->logits, BLUM_F32, HR));
     } else {
         TRY(blum_rmsnorm(ctx, xh, nullptr, m->out_norm, c.rms_eps, m->xn, nullptr, adt, HR, H));
         TRY(blum_q8_0_matmul(ctx, m->head, m->xn, adt, m->logits, BLUM_F32, HR));
@@ -215,18 +188,16 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
     if (c.tp_size > 1) {
         // vocabulary-parallel head: local (max, global index) per row, all-gather of the pairs, final pick
         TRY(blum_argmax_pairs(ctx, m->logits, HR, m->vocab, c.tp_rank * m->vocab, m->d_pairs + (size_t)c.tp_rank * HR * 2));
-        TRY(blum_allgather(ctx, m->comm, m->d_pairs + (size_t)c.tp_rank * HR * 2, m->d_pairs, (int64_t)HR * 8));
+        TRY(blum_allgather(ctx, m->comm, m->d_pairs + (size_t)c.tp_rank * HR * 2, m->d_pairs, (int64_t)HR * 8, 0));
         TRY(blum_pick_pairs(ctx, m->d_pairs, c.tp_size, HR, m->d_next));
         return BLUM_OK;
     }
-    if (!(skip & 64)) TRY(blum_argmax(ctx, m->logits, BLUM_F32, HR, m->vocab, m->d_next));
+    TRY(blum_argmax(ctx, m->logits, BLUM_F32, HR, m->vocab, m->d_next));
     return BLUM_OK;
 }
 
 static int pick_nsplit(const blum_ctx* ctx, const blum_llama* m, int R, int64_t max_ctx_len) {
     // enough CTAs for several waves (ragged context lengths balance out), but no split shorter than 256 positions
-    static const int forced = getenv("BLUM_ATTN_SPLITS") ? atoi(getenv("BLUM_ATTN_SPLITS")) : 0;   // measurement aid
-    if (forced > 0) return forced < m->max_splits ? forced : m->max_splits;
     int by_grid = (6 * ctx->sm_count + R * m->nkv - 1) / (R * m->nkv);
     int by_len = (int)((max_ctx_len + 255) / 256);
     int n = by_grid < by_len ? by_grid : by_len;

@@ -17,7 +17,7 @@
 
 #define GEMV_MAX_MT 4
 
-struct GemvParams {
+struct GemvF32Params {
     const int8_t* q;  const __half* d;     // weight (gate weight in SwiGLU mode)
     const int8_t* q2; const __half* d2;    // up weight in SwiGLU mode, else null
     const void* x;    void* y;
@@ -68,7 +68,7 @@ template <> __device__ __forceinline__ void load4_f32<__nv_bfloat16>(const __nv_
 
 // MT rows of x, R rows of W per warp pass, U chunks in flight.  SWIGLU: rows come in (gate, up) pairs.
 template <typename TX, typename TY, int MT, int R, int U, bool SWIGLU>
-__global__ void __launch_bounds__(256) q8_gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(256) q8_gemv_kernel(const GemvF32Params p) {
     extern __shared__ __align__(16) float xs[];   // [MT][KP]
     __shared__ float red[MT][8];
     __shared__ float rs_sh[MT];
@@ -194,17 +194,12 @@ __global__ void __launch_bounds__(256) q8_gemv_kernel(const GemvParams p) {
     }
 }
 
+// launch shape of the float form: rows per warp, 32-block steps in flight per lane, warps per CTA, CTAs per SM
 struct GemvVariant { int R, U, warps, ctas_per_sm; };
-// variant table for the development hook; index 0 is the dispatcher's default
-static const GemvVariant kVariants[] = {
-    {2, 2, 8, 2},  {1, 2, 8, 2},  {1, 4, 8, 2},  {2, 1, 8, 2},  {2, 4, 8, 2},  {4, 1, 8, 2},
-    {4, 2, 8, 2},  {2, 2, 8, 4},  {2, 2, 4, 4},  {4, 2, 8, 1},  {1, 4, 8, 4},  {2, 2, 8, 1},
-    {2, 4, 4, 4},  {4, 2, 4, 4},  {1, 4, 4, 8},  {2, 2, 8, 3},
-};
-static const int kNumVariants = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
+static const GemvVariant kGemvShape = {2, 2, 8, 2};
 
 template <typename TX, typename TY, int MT, int R, int U, bool SWIGLU>
-static int launch_one(blum_ctx* ctx, const GemvParams& p, int warps, int ctas_per_sm) {
+static int launch_one(blum_ctx* ctx, const GemvF32Params& p, int warps, int ctas_per_sm) {
     auto kern = q8_gemv_kernel<TX, TY, MT, R, U, SWIGLU>;
     const size_t smem = (size_t)MT * ((p.K + 511) & ~511) * sizeof(float);
     BLUM_REQUIRE(ctx, smem + 1024 <= ctx->smem_optin, "q8 gemv: K=%d with %d rows of x needs %zu B of shared memory", p.K, MT, smem);
@@ -220,21 +215,13 @@ static int launch_one(blum_ctx* ctx, const GemvParams& p, int warps, int ctas_pe
 }
 
 template <typename TX, typename TY, int MT, bool SWIGLU>
-static int launch_ru(blum_ctx* ctx, const GemvParams& p, const GemvVariant& v) {
-#define RU(r, u) if (v.R == r && v.U == u) return launch_one<TX, TY, MT, r, u, SWIGLU>(ctx, p, v.warps, v.ctas_per_sm)
-    if constexpr (SWIGLU) {
-        return launch_one<TX, TY, MT, 1, 2, true>(ctx, p, v.warps, v.ctas_per_sm);
-    } else if constexpr (MT == 1) {
-        RU(1, 2); RU(1, 4); RU(2, 1); RU(2, 4); RU(4, 1); RU(4, 2);
-        return launch_one<TX, TY, 1, 2, 2, false>(ctx, p, v.warps, v.ctas_per_sm);
-    } else {
-        return launch_one<TX, TY, MT, 2, 2, false>(ctx, p, v.warps, v.ctas_per_sm);
-    }
-#undef RU
+static int launch_ru(blum_ctx* ctx, const GemvF32Params& p, const GemvVariant& v) {
+    if constexpr (SWIGLU) return launch_one<TX, TY, MT, 1, 2, true>(ctx, p, v.warps, v.ctas_per_sm);
+    else return launch_one<TX, TY, MT, 2, 2, false>(ctx, p, v.warps, v.ctas_per_sm);
 }
 
 template <typename TX, typename TY, bool SWIGLU>
-static int launch_mt(blum_ctx* ctx, GemvParams p, const GemvVariant& v) {
+static int launch_mt(blum_ctx* ctx, GemvF32Params p, const GemvVariant& v) {
     // rows of x in chunks of up to GEMV_MAX_MT; W is re-read once per chunk
     // as many rows of x per pass as fit in shared memory as f32
     int max_mt = (int)((ctx->smem_optin - 2048) / ((size_t)((p.K + 511) & ~511) * sizeof(float)));
@@ -256,7 +243,7 @@ static int launch_mt(blum_ctx* ctx, GemvParams p, const GemvVariant& v) {
 }
 
 template <bool SWIGLU>
-static int launch_types(blum_ctx* ctx, const GemvParams& p, int xdt, int ydt, const GemvVariant& v) {
+static int launch_types(blum_ctx* ctx, const GemvF32Params& p, int xdt, int ydt, const GemvVariant& v) {
 #define TT(xd, yd, TX, TY) if (xdt == xd && ydt == yd) return launch_mt<TX, TY, SWIGLU>(ctx, p, v)
     TT(BLUM_F32, BLUM_F32, float, float);
     TT(BLUM_BF16, BLUM_BF16, __nv_bfloat16, __nv_bfloat16);
@@ -267,47 +254,27 @@ static int launch_types(blum_ctx* ctx, const GemvParams& p, int xdt, int ydt, co
     return blum_fail(ctx, BLUM_ERR_INVALID, "q8 gemv: unsupported dtype pair (%d,%d)", xdt, ydt);
 }
 
-// Chooses rows-per-warp so that there are enough row groups to occupy every warp of the grid.
-static GemvVariant pick_variant(const blum_ctx* ctx, int64_t N, int64_t K, bool swiglu) {
-    GemvVariant v = kVariants[0];
-    if (swiglu) { v.R = 1; v.U = 2; }
-    (void)ctx; (void)N; (void)K;
-    return v;
-}
-
 // integer-dot-product form (q8_gemv_i8.cu)
 bool blum_gemv_i8_supported(int xdt, int ydt);
-int blum_gemv_i8_num_variants();
 int blum_gemv_i8_dispatch(blum_ctx* ctx, const blum_q8_weight* w, const blum_q8_weight* w_up, const void* x, int xdt,
-                          const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M, int variant);
+                          const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M);
 
-// variant < 0: dispatcher's choice; [0, kNumVariants): float form; kNumVariants + i: integer form variant i
+// M <= 2 with a supported dtype pair takes the integer-dot-product kernel, everything else the float form
 int blum_gemv_dispatch(blum_ctx* ctx, const blum_q8_weight* w, const blum_q8_weight* w_up, const void* x, int xdt,
-                       const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M, int variant) {
-    if (variant >= kNumVariants)
-        return blum_gemv_i8_dispatch(ctx, w, w_up, x, xdt, norm_w, eps, residual, y, ydt, M, variant - kNumVariants);
-    if (variant < 0 && M <= 2 && blum_gemv_i8_supported(xdt, ydt))
-        return blum_gemv_i8_dispatch(ctx, w, w_up, x, xdt, norm_w, eps, residual, y, ydt, M, -1);
+                       const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M) {
+    if (M <= 2 && blum_gemv_i8_supported(xdt, ydt))
+        return blum_gemv_i8_dispatch(ctx, w, w_up, x, xdt, norm_w, eps, residual, y, ydt, M);
     BLUM_REQUIRE(ctx, w && x && y, "q8 matmul: null argument");
     BLUM_REQUIRE(ctx, M >= 1, "q8 matmul: M must be >= 1 (got %lld)", (long long)M);
     BLUM_REQUIRE(ctx, xdt >= 0 && xdt <= 2 && ydt >= 0 && ydt <= 2, "q8 matmul: bad dtype");
     BLUM_REQUIRE(ctx, w->N < (1ll << 31) && w->K < (1ll << 31), "q8 matmul: dimension too large");
     BLUM_REQUIRE(ctx, ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 4) == 0, "q8 matmul: x must be 16-byte aligned");
     if (w_up) BLUM_REQUIRE(ctx, w_up->N == w->N && w_up->K == w->K, "q8 swiglu: gate and up weights differ in shape");
-    GemvParams p;
+    GemvF32Params p;
     p.q = w->q; p.d = w->d;
     p.q2 = w_up ? w_up->q : nullptr; p.d2 = w_up ? w_up->d : nullptr;
     p.x = x; p.y = y; p.residual = residual; p.norm_w = norm_w; p.eps = eps;
     p.N = (int)w->N; p.K = (int)w->K; p.M = (int)M; p.m0 = 0; p.mt = 1;
-    GemvVariant v = (variant >= 0 && variant < kNumVariants) ? kVariants[variant] : pick_variant(ctx, w->N, w->K, w_up != nullptr);
-    if (w_up) { v.R = 1; v.U = 2; return launch_types<true>(ctx, p, xdt, ydt, v); }
-    return launch_types<false>(ctx, p, xdt, ydt, v);
-}
-
-extern "C" int blum_q8_0_gemv_variant(blum_ctx* ctx, int variant, const blum_q8_weight* w, const void* x,
-                                      blum_dtype x_dtype, void* y, blum_dtype y_dtype, int64_t M) {
-    if (!ctx) return BLUM_ERR_INVALID;
-    BLUM_REQUIRE(ctx, variant >= 0 && variant < kNumVariants + blum_gemv_i8_num_variants(), "gemv variant %d outside [0,%d)",
-                 variant, kNumVariants + blum_gemv_i8_num_variants());
-    return blum_gemv_dispatch(ctx, w, nullptr, x, x_dtype, nullptr, 0.f, nullptr, y, y_dtype, M, variant);
+    if (w_up) return launch_types<true>(ctx, p, xdt, ydt, kGemvShape);
+    return launch_types<false>(ctx, p, xdt, ydt, kGemvShape);
 }

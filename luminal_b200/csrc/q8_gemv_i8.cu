@@ -15,10 +15,8 @@
 //     reads 1 KiB contiguous per row per step; R rows x U steps are in flight per lane.
 // Algorithmic bytes per launch: N*K*34/32 + M*K*sizeof(x) + M*N*sizeof(y).
 #include "common.cuh"
-#include <stdio.h>
-#include <stdlib.h>
 
-struct GemvParams {
+struct GemvI8Params {
     const int8_t* q;  const __half* d;
     const int8_t* q2; const __half* d2;
     const void* x;    void* y;
@@ -70,7 +68,7 @@ __device__ __forceinline__ int limb_offset(int k, int plane) {
 }
 
 template <typename TX, typename TY, int MT, int R, int U, int THREADS, bool SWIGLU>
-__global__ void __launch_bounds__(THREADS) q8_gemv_i8_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(THREADS) q8_gemv_i8_kernel(const GemvI8Params p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float red[MT][THREADS / 32];
     __shared__ float rs_sh[MT];
@@ -288,17 +286,8 @@ __global__ void __launch_bounds__(THREADS) q8_gemv_i8_kernel(const GemvParams p)
     blum_trace(p.trace, 3);
 }
 
-struct I8Variant { int R, U, threads, ctas_per_sm; };
-static const I8Variant kI8Variants[] = {
-    {2, 2, 256, 4}, {2, 2, 512, 2}, {4, 1, 256, 4}, {4, 2, 256, 2}, {2, 4, 256, 2}, {1, 4, 256, 4},
-    {2, 1, 512, 2}, {4, 1, 512, 2}, {1, 2, 512, 2}, {2, 2, 256, 2}, {2, 2, 256, 3}, {1, 4, 512, 2},
-    {2, 2, 1024, 1}, {2, 1, 1024, 1}, {1, 2, 1024, 1}, {1, 4, 1024, 1},
-};
-static const int kNumI8Variants = (int)(sizeof(kI8Variants) / sizeof(kI8Variants[0]));
-int blum_gemv_i8_num_variants() { return kNumI8Variants; }
-
 template <typename TX, typename TY, int MT, int R, int U, int THREADS, bool SWIGLU>
-static int launch_i8(blum_ctx* ctx, const GemvParams& p, int ctas_per_sm) {
+static int launch_i8(blum_ctx* ctx, const GemvI8Params& p, int ctas_per_sm) {
     auto kern = q8_gemv_i8_kernel<TX, TY, MT, R, U, THREADS, SWIGLU>;
     const int nit = (p.K + 1023) >> 10;
     const size_t smem = (size_t)MT * nit * (3072 + 128);
@@ -321,33 +310,23 @@ static int launch_i8(blum_ctx* ctx, const GemvParams& p, int ctas_per_sm) {
     return BLUM_OK;
 }
 
+// One CTA of 32 warps per SM stages x once per SM; one row per warp pass keeps the row groups fine-grained; two
+// 32-weight blocks per lane in flight.  (Smaller CTAs that could share an SM with the next kernel were measured and
+// lose: half the warps cannot issue the dp4a work at stream rate.)
 template <typename TX, typename TY, int MT, bool SWIGLU>
-static int launch_i8_v(blum_ctx* ctx, const GemvParams& p, const I8Variant& v) {
-#define V(r, u, t) if (v.R == r && v.U == u && v.threads == t) return launch_i8<TX, TY, MT, r, u, t, SWIGLU>(ctx, p, v.ctas_per_sm)
-    if constexpr (SWIGLU) {
-        V(1, 2, 256); V(2, 1, 256); V(1, 2, 512); V(2, 2, 256); V(1, 2, 1024); V(1, 1, 1024);
-        return launch_i8<TX, TY, MT, 1, 2, 256, true>(ctx, p, v.ctas_per_sm);
-    } else if constexpr (MT == 1) {
-        V(2, 2, 256); V(2, 2, 512); V(4, 1, 256); V(4, 2, 256); V(2, 4, 256); V(1, 4, 256);
-        V(2, 1, 512); V(4, 1, 512); V(1, 2, 512); V(1, 4, 512); V(1, 2, 256);
-        V(2, 2, 1024); V(2, 1, 1024); V(1, 2, 1024); V(1, 4, 1024);
-        return launch_i8<TX, TY, 1, 2, 2, 256, false>(ctx, p, v.ctas_per_sm);
-    } else {
-        V(2, 2, 256); V(2, 1, 512); V(1, 2, 1024); V(1, 1, 1024);
-        return launch_i8<TX, TY, MT, 2, 2, 256, false>(ctx, p, v.ctas_per_sm);
-    }
-#undef V
+static int launch_i8_v(blum_ctx* ctx, const GemvI8Params& p) {
+    return launch_i8<TX, TY, MT, 1, 2, 1024, SWIGLU>(ctx, p, 1);
 }
 
 template <bool SWIGLU>
-static int launch_i8_types(blum_ctx* ctx, GemvParams p, int xdt, int ydt, const I8Variant& v) {
+static int launch_i8_types(blum_ctx* ctx, GemvI8Params p, int xdt, int ydt) {
     for (int m0 = 0; m0 < p.M; m0 += 2) {
         p.m0 = m0;
         p.mt = (p.M - m0 < 2) ? 1 : 2;
         int rc = BLUM_ERR_INVALID;
 #define TT(xd, yd, TX, TY)                                                                  \
         if (xdt == xd && ydt == yd)                                                         \
-            rc = (p.mt == 1) ? launch_i8_v<TX, TY, 1, SWIGLU>(ctx, p, v) : launch_i8_v<TX, TY, 2, SWIGLU>(ctx, p, v)
+            rc = (p.mt == 1) ? launch_i8_v<TX, TY, 1, SWIGLU>(ctx, p) : launch_i8_v<TX, TY, 2, SWIGLU>(ctx, p)
         TT(BLUM_F32, BLUM_F32, float, float);
         TT(BLUM_BF16, BLUM_BF16, __nv_bfloat16, __nv_bfloat16);
         TT(BLUM_F16, BLUM_F16, __half, __half);
@@ -359,35 +338,25 @@ static int launch_i8_types(blum_ctx* ctx, GemvParams p, int xdt, int ydt, const 
     return BLUM_OK;
 }
 
-// Default configuration per shape (from the operator sweep); the swiglu form keeps two weight streams in flight.
-static I8Variant pick_i8(const blum_ctx*, int64_t, int64_t, bool swiglu) {
-    // one CTA of 32 warps per SM stages x once per SM; one row per warp pass keeps the row groups fine-grained
-    static const char* env = getenv("BLUM_GEMV_PICK");      // measurement aid: "U,threads,ctas_per_sm,U_swiglu"
-    if (env) { int u = 2, t = 1024, c = 1, us = 2; sscanf(env, "%d,%d,%d,%d", &u, &t, &c, &us); return I8Variant{1, swiglu ? us : u, t, c}; }
-    if (swiglu) return I8Variant{1, 2, 1024, 1};
-    return I8Variant{1, 2, 1024, 1};
-}
-
 bool blum_gemv_i8_supported(int xdt, int ydt) {
     return (xdt == ydt) || (ydt == BLUM_F32 && xdt != BLUM_F32);
 }
 
 int blum_gemv_i8_dispatch(blum_ctx* ctx, const blum_q8_weight* w, const blum_q8_weight* w_up, const void* x, int xdt,
-                          const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M, int variant) {
+                          const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M) {
     BLUM_REQUIRE(ctx, w && x && y, "q8 matmul: null argument");
     BLUM_REQUIRE(ctx, M >= 1, "q8 matmul: M must be >= 1 (got %lld)", (long long)M);
     BLUM_REQUIRE(ctx, xdt >= 0 && xdt <= 2 && ydt >= 0 && ydt <= 2, "q8 matmul: bad dtype");
     BLUM_REQUIRE(ctx, w->N < (1ll << 31) && w->K < (1ll << 31), "q8 matmul: dimension too large");
     BLUM_REQUIRE(ctx, ((uintptr_t)x % 16) == 0, "q8 matmul: x must be 16-byte aligned");
     if (w_up) BLUM_REQUIRE(ctx, w_up->N == w->N && w_up->K == w->K, "q8 swiglu: gate and up weights differ in shape");
-    GemvParams p;
+    GemvI8Params p;
     p.q = w->q; p.d = w->d;
     p.q2 = w_up ? w_up->q : nullptr; p.d2 = w_up ? w_up->d : nullptr;
     p.x = x; p.y = y; p.residual = residual; p.norm_w = norm_w; p.eps = eps;
     p.N = (int)w->N; p.K = (int)w->K; p.M = (int)M; p.m0 = 0; p.mt = 1;
     p.trace = blum_trace_slot(ctx);
     ctx->err.clear();
-    const I8Variant v = (variant >= 0 && variant < kNumI8Variants) ? kI8Variants[variant] : pick_i8(ctx, w->N, w->K, w_up != nullptr);
-    if (w_up) return launch_i8_types<true>(ctx, p, xdt, ydt, v);
-    return launch_i8_types<false>(ctx, p, xdt, ydt, v);
+    if (w_up) return launch_i8_types<true>(ctx, p, xdt, ydt);
+    return launch_i8_types<false>(ctx, p, xdt, ydt);
 }

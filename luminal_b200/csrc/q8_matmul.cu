@@ -2,10 +2,9 @@
 // mma.sync kernel (3 <= M <= 16, bf16 activations) or the tcgen05 GEMM (larger M, tensor-core-bound).  Replaces QuantizedMatmul<T>::process
 // (crates/luminal_cuda/src/quantized.rs:116-168 in luminal).
 #include "common.cuh"
-#include <stdlib.h>
 
 int blum_gemv_dispatch(blum_ctx* ctx, const blum_q8_weight* w, const blum_q8_weight* w_up, const void* x, int xdt,
-                       const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M, int variant);
+                       const float* norm_w, float eps, const void* residual, void* y, int ydt, int64_t M);
 int blum_gemm_tc_supported(const blum_ctx* ctx, const blum_q8_weight* w, int xdt, int ydt, int64_t M);
 int blum_gemm_tc_dispatch(blum_ctx* ctx, const blum_q8_weight* w, const void* x, int xdt, void* y, int ydt, int64_t M);
 
@@ -22,12 +21,11 @@ int blum_q8_0_matmul(blum_ctx* ctx, const blum_q8_weight* w, const void* x, blum
                      int64_t M) {
     if (!ctx) return BLUM_ERR_INVALID;
     if (M == 0) return BLUM_OK;
-    static const int small_max = getenv("BLUM_SMALL_GEMM_MAX_M") ? atoi(getenv("BLUM_SMALL_GEMM_MAX_M")) : BLUM_GEMM_SMALL_MAX_M;   // measurement aid
-    if (M >= BLUM_GEMM_MIN_M && M <= small_max && w && blum_gemm_small_supported(w, xdt, ydt, M))
+    if (M >= BLUM_GEMM_MIN_M && M <= BLUM_GEMM_SMALL_MAX_M && w && blum_gemm_small_supported(w, xdt, ydt, M))
         return blum_gemm_small_dispatch(ctx, w, x, xdt, y, ydt, M);
     if (M >= BLUM_GEMM_MIN_M && w && blum_gemm_tc_supported(ctx, w, xdt, ydt, M))
         return blum_gemm_tc_dispatch(ctx, w, x, xdt, y, ydt, M);
-    return blum_gemv_dispatch(ctx, w, nullptr, x, xdt, nullptr, 0.f, nullptr, y, ydt, M, -1);
+    return blum_gemv_dispatch(ctx, w, nullptr, x, xdt, nullptr, 0.f, nullptr, y, ydt, M);
 }
 
 int blum_q8_0_matmul_fused(blum_ctx* ctx, const blum_q8_weight* w, const void* x, blum_dtype xdt,
@@ -35,17 +33,16 @@ int blum_q8_0_matmul_fused(blum_ctx* ctx, const blum_q8_weight* w, const void* x
                            int64_t M) {
     if (!ctx) return BLUM_ERR_INVALID;
     if (M == 0) return BLUM_OK;
-    return blum_gemv_dispatch(ctx, w, nullptr, x, xdt, norm_weight, eps, residual, y, ydt, M, -1);
+    return blum_gemv_dispatch(ctx, w, nullptr, x, xdt, norm_weight, eps, residual, y, ydt, M);
 }
 
 int blum_q8_0_matmul_timed(blum_ctx* ctx, blum_q8_weight* const* ws, int nws, const void* x, blum_dtype xdt, void* y,
-                           blum_dtype ydt, int64_t M, int variant, int iters, float* avg_us) {
+                           blum_dtype ydt, int64_t M, int iters, float* avg_us) {
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, ws && nws > 0 && iters > 0 && avg_us, "matmul_timed: bad argument");
     // one plain launch first: lets every path size its workspaces outside the capture
     {
-        const int rc0 = (variant >= 0) ? blum_gemv_dispatch(ctx, ws[0], nullptr, x, xdt, nullptr, 0.f, nullptr, y, ydt, M, variant)
-                                       : blum_q8_0_matmul(ctx, ws[0], x, xdt, y, ydt, M);
+        const int rc0 = blum_q8_0_matmul(ctx, ws[0], x, xdt, y, ydt, M);
         if (rc0) return rc0;
         BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
@@ -55,8 +52,7 @@ int blum_q8_0_matmul_timed(blum_ctx* ctx, blum_q8_weight* const* ws, int nws, co
     int rc = BLUM_OK;
     for (int i = 0; i < iters && !rc; i++) {
         const blum_q8_weight* w = ws[i % nws];
-        rc = (variant >= 0) ? blum_gemv_dispatch(ctx, w, nullptr, x, xdt, nullptr, 0.f, nullptr, y, ydt, M, variant)
-                            : blum_q8_0_matmul(ctx, w, x, xdt, y, ydt, M);
+        rc = blum_q8_0_matmul(ctx, w, x, xdt, y, ydt, M);
     }
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
     ctx->launches = launches_before;
@@ -88,7 +84,7 @@ int blum_q8_0_matmul_swiglu(blum_ctx* ctx, const blum_q8_weight* w_gate, const b
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, w_gate && w_up, "q8 swiglu: null weight");
     if (M == 0) return BLUM_OK;
-    return blum_gemv_dispatch(ctx, w_gate, w_up, x, xdt, norm_weight, eps, nullptr, y, ydt, M, -1);
+    return blum_gemv_dispatch(ctx, w_gate, w_up, x, xdt, norm_weight, eps, nullptr, y, ydt, M);
 }
 
 }  // extern "C"

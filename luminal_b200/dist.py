@@ -47,11 +47,12 @@ def tp_window(name, cfg, rank, size):
 class Comm:
     """NCCL communicator bound to one context (one GPU, one process)."""
 
-    def __init__(self, ctx, nranks, rank, unique_id: bytes):
+    def __init__(self, ctx, nranks, rank, unique_id: bytes, init_timeout_ms=120000):
+        """init_timeout_ms: give up (BlumError, ERR_COMM) if a rank has not joined in that time; 0 waits for ever."""
         assert len(unique_id) == 128
         self.ctx, self.nranks, self.rank = ctx, nranks, rank
         h = C.c_void_p()
-        ctx._check(ctx.lib.blum_comm_init_rank(ctx.h, nranks, rank, unique_id, C.byref(h)))
+        ctx._check(ctx.lib.blum_comm_init_rank(ctx.h, nranks, rank, unique_id, int(init_timeout_ms), C.byref(h)))
         self.h = h.value
 
     @staticmethod
@@ -79,17 +80,19 @@ class Comm:
             time.sleep(0.01)
         return open(path, "rb").read()
 
-    def allreduce_sum(self, buf, count, dtype):
-        self.ctx._check(self.ctx.lib.blum_allreduce_sum(self.ctx.h, self.h, buf.ptr, count, dtype))
+    # timeout_ms = 0 only enqueues the collective; > 0 waits for it and aborts the communicator if a peer never arrives
 
-    def allgather(self, send, recv, bytes_per_rank):
-        self.ctx._check(self.ctx.lib.blum_allgather(self.ctx.h, self.h, send.ptr, recv.ptr, bytes_per_rank))
+    def allreduce_sum(self, buf, count, dtype, timeout_ms=0):
+        self.ctx._check(self.ctx.lib.blum_allreduce_sum(self.ctx.h, self.h, buf.ptr, count, dtype, int(timeout_ms)))
 
-    def alltoallv(self, send, send_bytes, send_offsets, recv, recv_bytes, recv_offsets):
+    def allgather(self, send, recv, bytes_per_rank, timeout_ms=0):
+        self.ctx._check(self.ctx.lib.blum_allgather(self.ctx.h, self.h, send.ptr, recv.ptr, bytes_per_rank, int(timeout_ms)))
+
+    def alltoallv(self, send, send_bytes, send_offsets, recv, recv_bytes, recv_offsets, timeout_ms=0):
         """Variable all-to-all in bytes; the four lists are per-peer host values."""
         arr = lambda v: (C.c_int64 * self.nranks)(*[int(x) for x in v])
         self.ctx._check(self.ctx.lib.blum_alltoallv(self.ctx.h, self.h, send.ptr, arr(send_bytes), arr(send_offsets), recv.ptr,
-                                                    arr(recv_bytes), arr(recv_offsets)))
+                                                    arr(recv_bytes), arr(recv_offsets), int(timeout_ms)))
 
     def destroy(self):
         if self.h:

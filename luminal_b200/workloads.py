@@ -178,3 +178,42 @@ def moe_ep(ctx: Context, comm, rank, world, steps, warmup, tokens_per_rank=1024,
             "ms_per_step": ms, "dtype": "bf16", "data": "synthetic", "scaling": "weak",
             "config": {"workload": "MXFP4 MoE layer, %d experts top-%d over %d GPUs, %d tokens per GPU, hidden %d, intermediate %d (seed %d)"
                                    % (E, top_k, world, T, H, I, seed), "exchange": "NCCL send/recv all-to-all, counts through the host"}}
+
+
+SWEEP_SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096), (8192, 28672)]   # (K, N)
+SWEEP_MS = [1, 8, 64, 512, 4096]
+
+
+def sweep(ctx: Context, ms=None, shapes=None, dtype=BF16, iters=20, hbm_peak=6520.5, tc_peak=1646.8, l2_bytes=126 << 20):
+    """Operator sweep of the Q8_0 matmul (seed 1): achieved HBM GB/s and TFLOP/s per (M, K, N).  Each shape is timed on
+    the device over `iters` launches captured in one CUDA graph; the launches rotate through enough distinct weight
+    tensors to exceed the L2, so every launch streams its weights from HBM."""
+    import ctypes as C
+    from .runtime import Q8Weight
+    rows = []
+    esz = 4 if dtype == F32 else 2
+    for k, n in (shapes or SWEEP_SHAPES):
+        wbytes = n * k * 34 // 32
+        copies = max(2, min(16, (2 * l2_bytes + wbytes - 1) // wbytes))
+        ws = [Q8Weight.generate(ctx, 1, 7000 + i, n, k) for i in range(copies)]
+        arr = (C.c_void_p * copies)(*[w.h for w in ws])
+        for m in (ms or SWEEP_MS):
+            x = ctx.to_device(gen_normal(1, 5, m * k).reshape(m, k), dtype)
+            y = ctx.alloc(m * n * esz)
+            us = C.c_float()
+            ctx._check(ctx.lib.blum_q8_0_matmul_timed(ctx.h, arr, copies, x.ptr, dtype, y.ptr, dtype, m, iters, C.byref(us)))
+            t_ms = us.value / 1e3
+            nbytes = wbytes + m * k * esz + m * n * esz
+            flops = 2.0 * m * n * k
+            rows.append({"K": k, "N": n, "M": m, "us": round(us.value, 2), "GBps": round(nbytes / t_ms / 1e6, 1),
+                         "hbm_frac": round(nbytes / t_ms / 1e6 / hbm_peak, 3), "TFLOPs": round(flops / t_ms / 1e9, 2),
+                         "tc_frac": round(flops / t_ms / 1e9 / tc_peak, 4)})
+            x.free()
+            y.free()
+        for w in ws:
+            w.free()
+    ctx.check_device_error()
+    return {"metric": "q8_0_matmul_operator_sweep", "unit": "us per launch", "dtype": {F32: "f32", BF16: "bf16"}.get(dtype, "f16"),
+            "data": "synthetic", "config": {"workload": "Q8_0 matmul operator sweep (seed 1), bf16 in / f32 accumulate / bf16 out",
+                                              "l2": "launches rotate through weight copies larger than L2"},
+            "peaks": {"hbm_GBps": hbm_peak, "bf16_TFLOPs_burst": tc_peak}, "rows": rows}

@@ -9,7 +9,7 @@ from luminal_b200 import _lib, runtime
 
 
 def test_library_exports_every_declared_symbol():
-    protos = _lib.declared_functions()
+    protos = _lib.all_declared_functions()        # include/blum.h and include/blum_dev.h
     assert len(protos) >= 70
     raw = C.CDLL(_lib.LIB_PATH)
     missing = [n for n in protos if not hasattr(raw, n)]
@@ -18,6 +18,27 @@ def test_library_exports_every_declared_symbol():
                  "blum_attn_decode_paged", "blum_attn_prefill_paged", "blum_swiglu", "blum_argmax", "blum_llama_decode",
                  "blum_q8_0_weight_from_gguf_bytes"):
         assert must in protos
+
+
+def test_every_product_declaration_names_its_reference_counterpart():
+    """include/blum.h is the drop-in boundary: the comment that precedes a declaration (or the section comment above it)
+    cites the reference interface it stands in for (a path in the luminal tree) or says that there is none."""
+    import re
+    text = open(_lib.HEADER_PATH).read()
+    protos = _lib.declared_functions()
+    dev = _lib.declared_functions(_lib.DEV_HEADER_PATH)
+    assert not set(protos) & set(dev)
+    cite = re.compile(r"crates/|src/|examples/|[Nn]o counterpart|absent in the reference|reference has|reference's|luminal (has|hard-codes)")
+    uncited = []
+    for name in protos:
+        at = re.search(r"^(?:const\s+)?[A-Za-z_][\w \*]*\b%s\(" % name, text, flags=re.M).start()      # the declaration, not a mention
+        comments = re.findall(r"/\*.*?\*/", text[:at], flags=re.S)
+        # the nearest comment, or the nearest section comment (one that opens with a dashed rule)
+        nearest = comments[-1] if comments else ""
+        section = next((c for c in reversed(comments) if "-----" in c), "")
+        if not (cite.search(nearest) or cite.search(section)):
+            uncited.append(name)
+    assert not uncited, uncited
 
 
 def test_no_torch_types_in_signatures():
@@ -77,3 +98,26 @@ def test_product_has_no_oracle_dependency():
                 text = open(os.path.join(dirpath, f)).read()
                 for needle in ("import oracle", "from oracle", "liboracle", "oracle/", "oracle."):
                     assert needle not in text, (dirpath, f, needle)
+
+
+def test_rust_ffi_declarations_follow_the_header():
+    """luminal_b200/rust/src/ffi.rs is generated from include/blum.h: it must be the generator's current output, declare
+    every entry point of the header with the same number of arguments, and lib.rs may only call what it declares."""
+    import importlib.util
+    import re
+    here = os.path.dirname(os.path.abspath(__file__))
+    gen = os.path.join(here, "..", "luminal_b200", "rust", "gen_ffi.py")
+    spec = importlib.util.spec_from_file_location("gen_ffi", gen)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    text = open(mod.OUT).read()
+    assert text == mod.render(), "ffi.rs is stale: run python luminal_b200/rust/gen_ffi.py"
+    protos = _lib.declared_functions()
+    for name, (_, argtypes) in protos.items():
+        m = re.search(r"pub fn %s\(([^)]*)\)" % name, text)
+        assert m, name
+        nargs = len([a for a in m.group(1).split(",") if a.strip()])
+        assert nargs == len(argtypes), (name, nargs, len(argtypes))
+    lib_rs = open(os.path.join(os.path.dirname(mod.OUT), "lib.rs")).read()
+    for called in set(re.findall(r"ffi::(blum_[a-z0-9_]+)\(", lib_rs)):
+        assert called in protos, called
