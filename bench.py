@@ -25,6 +25,8 @@ CFG = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=143
            rms_eps=1e-5, rope_theta=500000.0)
 PROMPT_LEN = 32
 SEED = 0
+# DRAM bytes / algorithmic bytes of decode_stream_kernel, from the ncu capture summarised in profiles/decode_stream_8b_4layers.md
+NCU_TRAFFIC_RATIO = None
 
 
 def measured_peaks():
@@ -198,6 +200,31 @@ def kernel_table(ctx, model, lib, hbm_peak):
     return rows
 
 
+def tp_leg(ctx, rank, world, dist):
+    """The 70B-shape decoder sharded over the job's N GPUs (N = 1: unsharded, the denominator of the scaling efficiency):
+    batch 16, 1024-token prompts, bf16 activations and KV, all-reduce after o_proj and down_proj; and a small decoder's
+    greedy ids under the same sharding against the CPU oracle's golden ids."""
+    from luminal_b200 import workloads
+    comm = None
+    if world > 1:
+        import torch
+        from luminal_b200.dist import Comm
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(Comm.unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        comm = Comm(ctx, world, rank, bytes(uid.cpu().numpy().tobytes()), init_timeout_ms=60000)
+    out = {"tp_parity": workloads.tp_parity(ctx, comm, rank, world, os.path.join(ROOT, "tests", "golden", "oracle_vectors.npz"))}
+    rec = workloads.tp70b(ctx, comm, rank, world, steps=8, warmup=3)
+    keep = ("value", "unit", "ms_per_step", "steps", "weight_bytes_per_gpu", "achieved_weight_GBps_per_gpu", "allreduce_ms_per_step",
+            "allreduce_share", "prefill", "config", "dtype")
+    out["tp70b"] = {k: rec[k] for k in keep if k in rec}
+    out["tp70b"]["tp"] = world
+    if comm is not None:
+        comm.destroy()
+    return out
+
+
 def run_own(args, rank, world, local_rank):
     from luminal_b200 import F32, Context
     from luminal_b200.llama import Llama
@@ -248,6 +275,14 @@ def run_own(args, rank, world, local_rank):
     barrier()
     launches = ctx.launches - launches0
     ms_dev = max_over_ranks(ms_dev)
+    # the dominant kernel alone (CUDA events on the launching stream): the last step launched again, without argmax / feedback
+    stream_us = None
+    if lib.blum_llama_decode_path(ctx.h, model.h) == 2:
+        import ctypes as C
+        us = C.c_float()
+        ctx._check(lib.blum_llama_stream_kernel_us(ctx.h, model.h, max(args.steps, 8), C.byref(us)))
+        stream_us = us.value
+    ctx_at_timing = PROMPT_LEN + max(args.warmup, 3) + args.steps
     model.kv.seq_free(seq)
 
     # ---- end-to-end arm: one blum_llama_decode call per token, ids from pinned host memory, token read back.
@@ -271,46 +306,64 @@ def run_own(args, rank, world, local_rank):
     ms_e2e = max_over_ranks(ms_e2e)
     ctx.check_device_error()
 
+    ktab = kernel_table(ctx, model, lib, hbm_peak) if rank == 0 else None
+    wbytes = model.weight_bytes
+    model.destroy()
+    # ---- tensor parallelism over the same N GPUs (the 70B configuration) and its parity check: every rank takes part
+    tp = None
+    if not args.no_tp:
+        try:
+            tp = tp_leg(ctx, rank, world, dist)
+        except Exception as e:      # a secondary record must not cost the headline line
+            tp = {"error": repr(e)}
     if rank != 0:
-        model.destroy()
         if dist is not None:
             dist.destroy_process_group()
         return
-    ktab = kernel_table(ctx, model, lib, hbm_peak)
     dom, allk = ktab["gate_up_gemv_swiglu"], ktab["all_gemv_launches_of_a_step"]
-    wbytes = model.weight_bytes
     tok_s = world * args.steps / (ms_dev / 1e3)
+    # algorithmic bytes of one launch of the persistent decode kernel: every Q8_0 weight once, the norm weights, the
+    # embedding row, and the cached K/V rows of the context (f32) read plus the new row written
+    kv_bytes = CFG["layers"] * 2 * CFG["kv_heads"] * CFG["head_dim"] * 4 * (ctx_at_timing + 1)
+    stream_bytes = wbytes + (2 * CFG["layers"] + 1) * CFG["hidden"] * 4 + CFG["hidden"] * 4 + kv_bytes
+    if stream_us is not None:
+        gbps = stream_bytes / (stream_us * 1e-6) / 1e9
+        roof = {"bound": "hbm", "kernel": "decode_stream_kernel (the whole single-sequence step: 161 phases, one launch)",
+                "achieved": gbps, "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbps / hbm_peak,
+                "launch_us": stream_us, "algorithmic_bytes": stream_bytes,
+                # DRAM read + write of one launch, scaled by layer count from an ncu capture of a 4-layer model of the same widths
+                # (profiles/decode_stream_8b_4layers.md): traffic / algorithmic bytes measured there, times this launch's bytes
+                "traffic": int(stream_bytes * NCU_TRAFFIC_RATIO) if NCU_TRAFFIC_RATIO else None,
+                "traffic_kind": "scaled from an ncu capture of the same kernel on a 4-layer model of the same widths",
+                "frac_of_8TBps": gbps / 8000.0}
+    else:
+        roof = {"bound": "hbm", "kernel": "q8_gemv_i8_kernel, all launches of one decode step (M=1)",
+                "achieved": allk["GBps"], "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": allk["GBps"] / hbm_peak,
+                "traffic": int(dom["bytes"] * 62.54 / 62.46), "traffic_kind": "per launch of the gate/up instance, scaled from an ncu capture",
+                "frac_of_8TBps": allk["GBps"] / 8000.0}
     line = {
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "parallelism": "replicas x%d" % world, "l2": "weights per step (7.97 GB) exceed L2 (126 MB)",
-                   "kv": "f32 paged, page 16", "activations": "f32"},
-        "e2e": {"value": world * args.steps / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4},
+                   "kv": "f32 paged, page 16", "activations": "f32",
+                   "decode_path": "persistent kernel" if stream_us is not None else "per-op kernels in a CUDA graph"},
+        "e2e": {"value": world * args.steps / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 8},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        # traffic: dram read + write of one launch.  ncu measured 62.54 MB per launch on the single-matrix instance of this
-        # kernel (N=14336, K=4096: 62.46 MB algorithmic, profiles/q8_gemv_i8_4096x14336_m1.md); the gate/up launch streams two
-        # such matrices with the same access pattern, so its traffic is that ratio times its own algorithmic bytes.
         "prefill": {"tokens": PROMPT_LEN, "ms": ms_prefill, "tokens_per_s": world * PROMPT_LEN / (ms_prefill / 1e3),
                     "how": "blum_llama_prefill with host ids, wall clock around the call (H2D of ids and D2H of the first token inside)"},
-        # achieved: algorithmic bytes of ALL Q8_0 GEMV launches of one step (129 launches, five shapes) over their summed
-        # device time; best_instance is the largest single launch.  traffic: DRAM read + write per launch of the dominant
-        # instance, scaled from an ncu capture of the single-matrix launch of the same kernel (62.54 MB measured for
-        # 62.46 MB algorithmic, profiles/q8_gemv_i8_4096x14336_m1.md).
-        "roofline": {"bound": "hbm", "kernel": "q8_gemv_i8_kernel, all launches of one decode step (M=1)",
-                     "achieved": allk["GBps"], "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": allk["GBps"] / hbm_peak, "traffic": int(dom["bytes"] * 62.54 / 62.46),
-                     "traffic_kind": "per launch of the gate/up instance, scaled from an ncu capture of the single-matrix launch",
-                     "frac_of_8TBps": allk["GBps"] / 8000.0,
-                     "best_instance": {"kernel": "gate/up + SwiGLU, N=2x14336, K=4096", "achieved": dom["GBps"], "frac": dom["GBps"] / hbm_peak}},
+        "roofline": roof,
         "step_roofline": {"weight_bytes_per_token": wbytes, "achieved_GBps": wbytes * args.steps / (ms_dev / 1e3) / 1e9,
                           "frac_of_measured": wbytes * args.steps / (ms_dev / 1e3) / 1e9 / hbm_peak,
                           "frac_of_8TBps": wbytes * args.steps / (ms_dev / 1e3) / 1e9 / 8000.0},
+        # the operator-level GEMV entry points on the same matrices (what a luminal operator would call one by one)
         "kernels": ktab,
     }
-    model.destroy()
+    if tp is not None:
+        line["tp70b"] = tp.get("tp70b", tp)
+        line["tp_parity"] = tp.get("tp_parity")
     if not args.no_cpu and world == 1:
         try:
             line["cpu_baseline"] = cpu_decode_run(8, 1)[0]
@@ -381,6 +434,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel 70B record and its parity check")
     ap.add_argument("--workload", default="decode8b", choices=["decode8b", "serve64", "tp70b", "moe", "moe_ep", "sweep"],
                     help="decode8b (default, the headline metric) or one of the secondary configurations")
     ap.add_argument("--layers", type=int, default=None, help="secondary workloads only: truncate the model to this many layers")

@@ -146,6 +146,12 @@ int blum_gather(blum_ctx* ctx, const void* table, blum_dtype table_dtype, int64_
  * With `residual` non-null: s = x + residual is written to sum_out (may alias x) and normalised. */
 int blum_rmsnorm(blum_ctx* ctx, const void* x, const void* residual, const float* weight, float eps,
                  void* y, void* sum_out, blum_dtype dtype, int64_t rows, int64_t dim);
+/* Per-head RMSNorm (optional) followed by rotary embedding, in place on the q and k heads of fused rows
+ * qkv [T, (q_heads + 2*kv_heads) * head_dim]: the glue of the qwen decoder (examples/qwen/src/model.rs:52-77,93-105).
+ * norm weights f32 [head_dim] or NULL (no norm); rope_mode as in blum_llama_cfg; v is left as it is. */
+int blum_qk_norm_rope(blum_ctx* ctx, void* qkv, blum_dtype dtype, const int32_t* positions, int64_t T, int q_heads,
+                      int kv_heads, int head_dim, const float* q_norm_w, const float* k_norm_w, float eps, float theta,
+                      int rope_mode);
 /* Interleaved-pair rotary embedding of examples/llama/src/model.rs:52-72 applied in place to
  * x [T, heads, head_dim]; positions int32 [T]. */
 int blum_rope_interleaved(blum_ctx* ctx, void* x, blum_dtype dtype, const int32_t* positions,
@@ -304,6 +310,12 @@ typedef struct blum_llama_cfg {
     int64_t kv_pages;        /* pages in the pool (0 = max_seqs * ceil(max_ctx/page_size)) */
     int32_t embed_q8;        /* 1: embedding table is Q8_0, 0: f32 */
     int32_t tp_rank, tp_size;/* tensor-parallel shard of this object (0,1 = unsharded) */
+    /* the sibling decoders of examples/llama: all zero = Llama */
+    int32_t rope_mode;       /* 0: interleaved pairs (x[2i], x[2i+1]) as examples/llama/src/model.rs:52-72 and examples/phi/src/model.rs:50-70;
+                                1: half-split pairs (x[i], x[i+d/2]) as examples/qwen/src/model.rs:52-77 */
+    int32_t qk_norm;         /* 1: per-head RMSNorm with weight on q and k before RoPE (examples/qwen/src/model.rs:93-105,160-161);
+                                tensors blk.N.attn_q_norm.weight / attn_k_norm.weight, f32 [head_dim] */
+    int32_t tie_head;        /* 1: logits = x * token_embd^T (examples/qwen/src/model.rs:233: embedding.reverse); needs embed_q8 = 1, no output.weight */
 } blum_llama_cfg;
 
 int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out);

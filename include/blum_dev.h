@@ -57,6 +57,9 @@ int blum_mxfp4_weight_generate(blum_ctx* ctx, uint64_t seed, uint64_t tensor_id,
  * tensor ids follow blum_llama_tensor_id(). */
 int blum_llama_generate_weights(blum_ctx* ctx, blum_llama* m, uint64_t seed);
 
+/* Average device time (CUDA events) of the persistent decode kernel alone: the step run last is launched `iters` more
+ * times (see csrc/llama.cu). */
+int blum_llama_stream_kernel_us(blum_ctx* ctx, blum_llama* m, int iters, float* avg_us);
 /* Development aid: average per-CTA cycle counters of the persistent decode kernel (see csrc/llama.cu). */
 int blum_llama_stream_profile(blum_ctx* ctx, blum_llama* m, double* out, int per_cta);
 

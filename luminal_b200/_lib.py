@@ -34,6 +34,7 @@ class LlamaCfg(C.Structure):
         ("act_dtype", C.c_int32), ("kv_dtype", C.c_int32), ("page_size", C.c_int32),
         ("max_seqs", C.c_int32), ("max_ctx", C.c_int32), ("kv_pages", C.c_int64),
         ("embed_q8", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32),
+        ("rope_mode", C.c_int32), ("qk_norm", C.c_int32), ("tie_head", C.c_int32),
     ]
 
 

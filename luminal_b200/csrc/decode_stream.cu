@@ -78,7 +78,7 @@ __device__ __forceinline__ uint32_t ds_tag_of(unsigned long long w) { return (ui
 __device__ __forceinline__ float ds_val_of(unsigned long long w) { return __uint_as_float((uint32_t)w); }
 
 // The first wait that gives up also records where: ctr[3] = site (1 weight stage, 2 activation word, 3 attention
-// input, 4 partial sums of a split group), ctr[4] = CTA, ctr[5], ctr[6] = what it waited for and what it saw.
+// input, 4 partial sums of a split group, 6 a slot of the per-unit sums), ctr[4] = CTA, ctr[5], ctr[6] = what it waited for and what it saw.
 __device__ __noinline__ void ds_give_up(int* err, unsigned long long* ctr, volatile int* s_abort, int site, long long a, long long b) {
     *s_abort = 1;
     atomicOr(err, 0x400);
@@ -131,6 +131,7 @@ struct DsShared {
     uint64_t full[DS_STAGES];
     float partial[DS_PARTIAL_SLOTS][16];            // per-unit row sums waiting for the rest of their group
     int gcnt[DS_PARTIAL_SLOTS];                     // units of a group deposited so far (indexed by group % slots)
+    int pbusy[DS_PARTIAL_SLOTS];                    // 1 while a slot of `partial` holds sums that have not been added up yet
     float wred[DS_WARPS];                           // sum of squares per warp
     float q[128], knew[128], vnew[128];
     float rsn[64], rcs[64];                         // rotation of the step's position
@@ -494,7 +495,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
         sh.seq = *reinterpret_cast<volatile unsigned long long*>(p.ctr + 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid_c; i < DS_PARTIAL_SLOTS; i += DS_THREADS) sh.gcnt[i] = 0;
+    for (int i = tid_c; i < DS_PARTIAL_SLOTS; i += DS_THREADS) { sh.gcnt[i] = 0; sh.pbusy[i] = 0; }
     __syncthreads();
 
     // ---- the weight stream.  Unit number n of this CTA's stream (all phases, in order) lives in ring stage n % NS, and
@@ -643,6 +644,17 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
             const long long g0c = clock64();
             const float p2_lo = __shfl_down_sync(0xffffffffu, acc0, 1), p2_hi = __shfl_down_sync(0xffffffffu, acc2, 1);
             const int pslot = n & (DS_PARTIAL_SLOTS - 1);
+            // The warps are not coupled to each other: one whose units keep hitting L2 can run many units ahead of one whose
+            // copy is late.  A slot of `partial` is therefore taken only once the group that used it before has been added up.
+            if (lane == 0 && *reinterpret_cast<volatile int*>(&sh.pbusy[pslot]) && !*s_abort) {
+                const unsigned long long t0 = blum_globaltimer();
+                for (uint32_t spin = 1; *reinterpret_cast<volatile int*>(&sh.pbusy[pslot]); spin++)
+                    if ((spin & 255u) == 0u && (ds_aborted(p, s_abort) || blum_globaltimer() - t0 > DS_TIMEOUT_NS)) {
+                        if (!*s_abort) ds_give_up(p.err, p.ctr, s_abort, 6, n, grp);
+                        break;
+                    }
+            }
+            __syncwarp();
             if (t == 0) {
                 sh.partial[pslot][g] = fmaf(acc0, 65536.f, fmaf(acc1, 256.f, p2_lo));
                 sh.partial[pslot][g + 8] = fmaf(acc2, 65536.f, fmaf(acc3, 256.f, p2_hi));
@@ -652,6 +664,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
             __syncwarp();
             int last = 0;
             if (lane == 0) {
+                sh.pbusy[pslot] = 1;
                 __threadfence_block();
                 const int gi = grp & (DS_PARTIAL_SLOTS - 1);
                 last = (atomicAdd(&sh.gcnt[gi], 1) == (seg_end - seg_first) - 1);
@@ -664,6 +677,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
                 if (lane < 16)
                     for (int uu = seg_first; uu < seg_end; uu++)             // fixed order: reproducible bit for bit
                         v += sh.partial[(nbase + (uu - u0)) & (DS_PARTIAL_SLOTS - 1)][lane];
+                __syncwarp();                                                // every lane has read the slots: hand them back
+                if (lane == 0) {
+                    __threadfence_block();
+                    for (int uu = seg_first; uu < seg_end; uu++) sh.pbusy[(nbase + (uu - u0)) & (DS_PARTIAL_SLOTS - 1)] = 0;
+                }
                 const bool has_head = (seg_first == grp * S), has_tail = (seg_end == (grp + 1) * S);
                 if (!has_head) {
                     // a later slice range of a group that starts in an earlier CTA: publish the partial sums

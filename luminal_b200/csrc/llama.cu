@@ -26,6 +26,7 @@
 struct LayerW {
     float* attn_norm = nullptr;
     float* ffn_norm = nullptr;
+    float *q_norm = nullptr, *k_norm = nullptr;     // per-head norm weights [head_dim] (qk_norm models)
     blum_q8_weight *wqkv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr, *wdown = nullptr;
 };
 
@@ -43,6 +44,7 @@ struct StreamPlan {
     unsigned long long* ctr = nullptr;
     size_t ctr_bytes = 0;
     long long* prof = nullptr;             // development aid (blum_llama_stream_profile)
+    int64_t last_ctx_len = 1;              // context length of the last launch (blum_llama_stream_kernel_us)
 };
 #define DS_MAX_SPLITS 16
 
@@ -130,11 +132,19 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
             if (l == 0) TRY(blum_rmsnorm(ctx, m->x, nullptr, w.attn_norm, c.rms_eps, m->xn, nullptr, adt, R, H));
             TRY(blum_q8_0_matmul(ctx, w.wqkv, m->xn, adt, m->qkv, adt, R));
         }
+        // The sibling decoders (per-head q/k norm, half-split rotary pairs) get their glue from one extra kernel that works in
+        // place on the fused rows; the kernels after it then rotate by zero angles.
+        float theta = c.rope_theta;
+        if (c.qk_norm || c.rope_mode != 0) {
+            TRY(blum_qk_norm_rope(ctx, m->qkv, adt, pos, R, m->nq, m->nkv, d, c.qk_norm ? w.q_norm : nullptr, c.qk_norm ? w.k_norm : nullptr,
+                                  c.rms_eps, c.rope_theta, c.rope_mode));
+            theta = 0.f;
+        }
         if (!last_row_only) {
             // decode: every row is the next token of its own sequence -> RoPE + append + attention in one launch
-            TRY(blum_attn_decode_fused(ctx, m->kv, l, m->qkv, adt, m->nq, c.rope_theta, seq, ctxl, R, nsplit, m->attn_scratch, m->attn));
+            TRY(blum_attn_decode_fused(ctx, m->kv, l, m->qkv, adt, m->nq, theta, seq, ctxl, R, nsplit, m->attn_scratch, m->attn));
         } else {
-            TRY(blum_rope_kv_append(ctx, m->kv, l, m->qkv, adt, m->nq, c.rope_theta, seq, pos, R, m->q));
+            TRY(blum_rope_kv_append(ctx, m->kv, l, m->qkv, adt, m->nq, theta, seq, pos, R, m->q));
             if (m->pre_seq >= 0 && blum_attn_prefill_mma_covers(adt, m->kv->dtype, d, m->kv->page_size))
                 TRY(blum_attn_prefill_mma(ctx, m->kv, l, m->q, adt, m->nq, m->pre_seq, m->pre_p0, R, m->attn));
             else
@@ -210,7 +220,7 @@ static bool stream_supported(blum_ctx* ctx, blum_llama* m) {
     if (m->stream_state >= 0) return m->stream_state == 1;
     const blum_llama_cfg& c = m->cfg;
     const int d = c.head_dim, H = c.hidden, qd = m->nq * d;
-    bool ok = c.tp_size == 1 && c.act_dtype == BLUM_F32 && c.kv_dtype == BLUM_F32 && d == 128 && !c.embed_q8;
+    bool ok = c.tp_size == 1 && c.act_dtype == BLUM_F32 && c.kv_dtype == BLUM_F32 && d == 128 && !c.embed_q8 && !c.qk_norm && c.rope_mode == 0 && !c.tie_head;
     ok = ok && H % DS_UNIT_K == 0 && qd % DS_UNIT_K == 0 && m->ffn % DS_UNIT_K == 0 && 5 * c.layers + 1 <= DS_MAX_PHASES;
     ok = ok && ((m->nq + 2 * m->nkv) * d) % DS_UNIT_ROWS == 0 && H % DS_UNIT_ROWS == 0 && m->ffn % 8 == 0 && m->vocab % DS_UNIT_ROWS == 0;
     int coop = 0;
@@ -295,9 +305,10 @@ static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
     return BLUM_OK;
 }
 
-static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
+static int run_stream_launch(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
     StreamPlan& sp = m->sp;
     if (!sp.built || sp.weights_version != m->weights_version) TRY(build_stream_plan(ctx, m));
+    sp.last_ctx_len = max_ctx_len;
     const blum_llama_cfg& c = m->cfg;
     DsParams p = {};
     p.phases = sp.d_phases; p.nphases = sp.nphases;
@@ -314,7 +325,10 @@ static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
     p.err = ctx->dev_error;
     p.prof = sp.prof;
     p.prof_layer = 3;
-    TRY(blum_ds_launch(ctx, p));
+    return blum_ds_launch(ctx, p);
+}
+static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
+    TRY(run_stream_launch(ctx, m, max_ctx_len));
     return blum_argmax(ctx, m->logits, BLUM_F32, 1, m->vocab, m->d_next);
 }
 
@@ -361,13 +375,19 @@ static bool resolve_tensor(blum_llama* m, const char* name, TensorRef* r) {
         return true;
     }
     if (!strcmp(name, "output_norm.weight")) { r->f32 = m->out_norm; r->f32_n = H; return true; }
-    if (!strcmp(name, "output.weight")) { *r = TensorRef{m->head, 0, m->vocab, H, (int64_t)rk * m->vocab, 0, nullptr, 0, false}; return true; }
+    if (!strcmp(name, "output.weight")) {
+        if (c.tie_head) return false;            // the head is the embedding table
+        *r = TensorRef{m->head, 0, m->vocab, H, (int64_t)rk * m->vocab, 0, nullptr, 0, false};
+        return true;
+    }
     int l = -1; char rest[64];
     if (sscanf(name, "blk.%d.%63s", &l, rest) != 2 || l < 0 || l >= c.layers) return false;
     LayerW& w = m->L[l];
     const int64_t nq_rows = (int64_t)m->nq * d, nkv_rows = (int64_t)m->nkv * d;
     if (!strcmp(rest, "attn_norm.weight")) { r->f32 = w.attn_norm; r->f32_n = H; return true; }
     if (!strcmp(rest, "ffn_norm.weight")) { r->f32 = w.ffn_norm; r->f32_n = H; return true; }
+    if (c.qk_norm && !strcmp(rest, "attn_q_norm.weight")) { r->f32 = w.q_norm; r->f32_n = d; return true; }
+    if (c.qk_norm && !strcmp(rest, "attn_k_norm.weight")) { r->f32 = w.k_norm; r->f32_n = d; return true; }
     if (!strcmp(rest, "attn_q.weight")) { *r = TensorRef{w.wqkv, 0, nq_rows, H, rk * nq_rows, 0, nullptr, 0, false}; return true; }
     if (!strcmp(rest, "attn_k.weight")) { *r = TensorRef{w.wqkv, nq_rows, nkv_rows, H, rk * nkv_rows, 0, nullptr, 0, false}; return true; }
     if (!strcmp(rest, "attn_v.weight")) { *r = TensorRef{w.wqkv, nq_rows + nkv_rows, nkv_rows, H, rk * nkv_rows, 0, nullptr, 0, false}; return true; }
@@ -398,10 +418,12 @@ int blum_llama_destroy(blum_ctx* ctx, blum_llama* m) {
     for (auto& w : m->L) {
         if (w.attn_norm) cudaFree(w.attn_norm);
         if (w.ffn_norm) cudaFree(w.ffn_norm);
+        if (w.q_norm) cudaFree(w.q_norm);
+        if (w.k_norm) cudaFree(w.k_norm);
         blum_q8_0_weight_free(ctx, w.wqkv); blum_q8_0_weight_free(ctx, w.wo); blum_q8_0_weight_free(ctx, w.wgate);
         blum_q8_0_weight_free(ctx, w.wup); blum_q8_0_weight_free(ctx, w.wdown);
     }
-    blum_q8_0_weight_free(ctx, m->head);
+    if (!m->cfg.tie_head) blum_q8_0_weight_free(ctx, m->head);
     blum_q8_0_weight_free(ctx, m->embed_q8);
     void* bufs[] = {m->embed_f32, m->out_norm, m->x, m->xn, m->qkv, m->q, m->attn, m->mid, m->gate, m->up, m->logits,
                     m->d_rows, m->d_next, m->d_hist, m->attn_scratch, m->d_pairs};
@@ -427,6 +449,9 @@ int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out
     BLUM_REQUIRE(ctx, c.page_size > 0 && c.max_seqs > 0 && c.max_ctx > 0, "llama_create: bad cache geometry");
     const int tp = c.tp_size > 0 ? c.tp_size : 1;
     BLUM_REQUIRE(ctx, c.tp_rank >= 0 && c.tp_rank < tp, "llama_create: tp_rank outside [0,tp_size)");
+    BLUM_REQUIRE(ctx, (c.rope_mode == 0 || c.rope_mode == 1) && (c.qk_norm == 0 || c.qk_norm == 1) && (c.tie_head == 0 || c.tie_head == 1),
+                 "llama_create: rope_mode, qk_norm and tie_head must be 0 or 1");
+    BLUM_REQUIRE(ctx, !c.tie_head || (c.embed_q8 && tp == 1), "llama_create: a tied head needs a Q8_0 embedding table (embed_q8 = 1) and no tensor parallelism");
     BLUM_REQUIRE(ctx, c.kv_heads % tp == 0 && c.ffn % (32 * tp) == 0 && c.vocab % tp == 0,
                  "llama_create: kv_heads, ffn/32 and vocab must divide by tp_size=%d", tp);
     BLUM_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -441,11 +466,13 @@ int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out
     if (c.embed_q8) { rc = blum_q8_alloc(ctx, c.vocab, H, &m->embed_q8); if (rc) return fail(rc); }
     else ALLOC(m->embed_f32, (size_t)c.vocab * H * 4);
     ALLOC(m->out_norm, (size_t)H * 4);
-    rc = blum_q8_alloc(ctx, m->vocab, H, &m->head); if (rc) return fail(rc);
+    if (c.tie_head) m->head = m->embed_q8;        // borrowed: freed once, as the embedding
+    else { rc = blum_q8_alloc(ctx, m->vocab, H, &m->head); if (rc) return fail(rc); }
     m->L.resize(c.layers);
     for (auto& w : m->L) {
         ALLOC(w.attn_norm, (size_t)H * 4);
         ALLOC(w.ffn_norm, (size_t)H * 4);
+        if (c.qk_norm) { ALLOC(w.q_norm, (size_t)d * 4); ALLOC(w.k_norm, (size_t)d * 4); }
         if ((rc = blum_q8_alloc(ctx, (int64_t)(m->nq + 2 * m->nkv) * d, H, &w.wqkv))) return fail(rc);
         if ((rc = blum_q8_alloc(ctx, H, (int64_t)m->nq * d, &w.wo))) return fail(rc);
         if ((rc = blum_q8_alloc(ctx, m->ffn, H, &w.wgate))) return fail(rc);
@@ -541,6 +568,29 @@ int blum_llama_stream_profile(blum_ctx* ctx, blum_llama* m, double* out, int per
     if (per_cta) for (size_t i = 0; i < n; i++) out[96 + i] = (double)h[i];      // [grid][32] counters, then [grid][64] timeline of one layer
     return BLUM_OK;
 }
+// Development aid: average device time of the persistent decode kernel alone.  The step that was run last is launched again
+// `iters` times between two CUDA events (same token, same position: every launch recomputes the same step and rewrites the
+// same KV slot with the same values), without the argmax and token feedback kernels that follow it in a real step.
+int blum_llama_stream_kernel_us(blum_ctx* ctx, blum_llama* m, int iters, float* avg_us) {
+    if (!ctx || !m || !avg_us || iters < 1) return BLUM_ERR_INVALID;
+    if (m->decode_path == 1 || !stream_supported(ctx, m) || !m->sp.built)
+        return blum_fail(ctx, BLUM_ERR_STATE, "stream kernel timing: run a single-sequence decode step on the persistent path first");
+    cudaEvent_t a, b;
+    BLUM_CUDA(ctx, cudaEventCreate(&a));
+    BLUM_CUDA(ctx, cudaEventCreate(&b));
+    int rc = BLUM_OK;
+    cudaEventRecord(a, ctx->stream);
+    for (int i = 0; i < iters && !rc; i++) rc = run_stream_launch(ctx, m, m->sp.last_ctx_len);
+    cudaEventRecord(b, ctx->stream);
+    const cudaError_t e = cudaEventSynchronize(b);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, a, b);
+    cudaEventDestroy(a); cudaEventDestroy(b);
+    if (rc) return rc;
+    if (e != cudaSuccess) return blum_fail(ctx, BLUM_ERR_CUDA, "stream kernel timing: %s", cudaGetErrorString(e));
+    *avg_us = ms * 1000.f / (float)iters;
+    return blum_check_device_error(ctx);
+}
 int blum_llama_set_comm(blum_ctx* ctx, blum_llama* m, blum_comm* comm) {
     if (!ctx || !m) return BLUM_ERR_INVALID;
     m->comm = comm;
@@ -551,8 +601,12 @@ int blum_llama_generate_weights(blum_ctx* ctx, blum_llama* m, uint64_t seed) {
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, m != nullptr, "llama_generate_weights: null model");
     m->weights_version++;
-    std::vector<std::string> names = {"token_embd.weight", "output_norm.weight", "output.weight"};
-    for (int l = 0; l < m->cfg.layers; l++) layer_names(l, &names);
+    std::vector<std::string> names = {"token_embd.weight", "output_norm.weight"};
+    if (!m->cfg.tie_head) names.push_back("output.weight");
+    for (int l = 0; l < m->cfg.layers; l++) {
+        layer_names(l, &names);
+        if (m->cfg.qk_norm) { names.push_back("blk." + std::to_string(l) + ".attn_q_norm.weight"); names.push_back("blk." + std::to_string(l) + ".attn_k_norm.weight"); }
+    }
     std::vector<float> host;
     for (const std::string& name : names) {
         TensorRef r;

@@ -122,9 +122,43 @@ __global__ void rope_kernel(T* __restrict__ x, const int32_t* __restrict__ posit
     }
 }
 
+// Per-head RMSNorm (optional) + RoPE of the q and k heads of fused qkv rows, in place: one warp per (token, head).
+// Values are rounded to the activation type where the reference's ops would round them (after the norm, after the rotation).
+template <typename T>
+__global__ void qk_norm_rope_kernel(T* __restrict__ qkv, const int32_t* __restrict__ positions, int64_t T_, int nq, int nkv, int d,
+                                    const float* __restrict__ qw, const float* __restrict__ kw, float eps, const RopeFreqs f, int mode) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int heads = nq + nkv, row = (nq + 2 * nkv) * d, half = d >> 1;
+    for (int64_t i = warp; i < T_ * heads; i += nwarps) {
+        const int64_t t = i / heads;
+        const int h = (int)(i - t * heads);
+        T* p = qkv + t * row + (int64_t)h * d;
+        const float* w = h < nq ? qw : kw;
+        float rs = 1.f;
+        if (w) {
+            float ss = 0.f;
+            for (int c = lane; c < d; c += 32) { const float v = to_f32<T>(p[c]); ss += v * v; }
+            rs = rsqrtf(warp_sum(ss) / (float)d + eps);
+        }
+        const float pos = (float)positions[t];
+        for (int pi = lane; pi < half; pi += 32) {
+            const int i0 = mode == 0 ? 2 * pi : pi, i1 = mode == 0 ? 2 * pi + 1 : pi + half;
+            float x0 = to_f32<T>(p[i0]), x1 = to_f32<T>(p[i1]);
+            if (w) { x0 = to_f32<T>(from_f32<T>(x0 * rs * w[i0])); x1 = to_f32<T>(from_f32<T>(x1 * rs * w[i1])); }
+            const float a = pos * f.inv_freq[pi];
+            const float sn = sinf(a), cs = sinf(1.5707964f - a);
+            p[i0] = from_f32<T>(x0 * cs - x1 * sn);
+            p[i1] = from_f32<T>(x1 * cs + x0 * sn);
+        }
+    }
+}
+
 void blum_rope_freqs(float theta, int head_dim, RopeFreqs* f) {
     // f_i = recip(exp(((2 i) * (1/d)) * ln(theta))) in f32, as examples/llama/src/model.rs:56-57 with
     // F32Pow = exp(t * ln|base|) (src/hl_ops/binary.rs:301-309)
+    // theta <= 0 asks for no rotation at all (all angles zero): the rotation was applied by an earlier kernel
+    if (!(theta > 0.f)) { for (int i = 0; i < 128; i++) f->inv_freq[i] = 0.f; return; }
     const float ln_theta = logf(fabsf(theta));
     const float inv_d = 1.0f / (float)head_dim;
     for (int i = 0; i < head_dim / 2 && i < 128; i++) {
@@ -359,6 +393,23 @@ int blum_rope_interleaved(blum_ctx* ctx, void* x, blum_dtype dt, const int32_t* 
     blum_rope_freqs(theta, head_dim, &f);
     const int64_t total = T * heads * (head_dim / 2);
     BLUM_DISPATCH_DTYPE(dt, TT, (rope_kernel<TT><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>((TT*)x, positions, T, heads, head_dim, f)));
+    BLUM_LAUNCH_CHECK(ctx);
+    return BLUM_OK;
+}
+
+int blum_qk_norm_rope(blum_ctx* ctx, void* qkv, blum_dtype dt, const int32_t* positions, int64_t T, int q_heads, int kv_heads,
+                      int head_dim, const float* q_norm_w, const float* k_norm_w, float eps, float theta, int rope_mode) {
+    if (!ctx) return BLUM_ERR_INVALID;
+    BLUM_REQUIRE(ctx, qkv && positions && T >= 0 && q_heads > 0 && kv_heads > 0, "qk_norm_rope: bad argument");
+    BLUM_REQUIRE(ctx, head_dim > 0 && head_dim % 2 == 0 && head_dim <= 256, "qk_norm_rope: head_dim %d not supported", head_dim);
+    BLUM_REQUIRE(ctx, rope_mode == 0 || rope_mode == 1, "qk_norm_rope: rope_mode must be 0 (interleaved) or 1 (half-split)");
+    BLUM_REQUIRE(ctx, (q_norm_w == nullptr) == (k_norm_w == nullptr), "qk_norm_rope: give both norm weights or neither");
+    if (T == 0) return BLUM_OK;
+    RopeFreqs f;
+    blum_rope_freqs(theta, head_dim, &f);
+    const int64_t warps = T * (q_heads + kv_heads);
+    BLUM_DISPATCH_DTYPE(dt, TT, (qk_norm_rope_kernel<TT><<<grid_for(ctx, warps * 32, 256), 256, 0, ctx->stream>>>(
+        (TT*)qkv, positions, T, q_heads, kv_heads, head_dim, q_norm_w, k_norm_w, eps, f, rope_mode)));
     BLUM_LAUNCH_CHECK(ctx);
     return BLUM_OK;
 }

@@ -69,6 +69,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1;
     return false;
 }
+// Drain wait of the abort path: no early exit on the abort flag, bounded by the global timer (nanoseconds).
+__device__ __forceinline__ bool mbar_wait_until(uint64_t* bar, uint32_t parity, uint64_t deadline_ns) {
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        uint64_t now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now > deadline_ns) return false;
+    }
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
@@ -128,7 +140,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     using C = GtCfg<TN, WF>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t full[8], a_ready[8], empty[8], acc_full;
+    __shared__ __align__(8) uint64_t full[8], a_ready[8], empty[8], acc_full, drained;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_flag;
     __shared__ uint32_t fp4_lut[WF == WF_MXFP4 ? 256 : 1];   // byte (two nibbles) -> two bf16 values
@@ -158,6 +170,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&a_ready[s], GT_CONV_WARPS); mbar_init(&empty[s], 1); }
         mbar_init(&acc_full, 1);
+        mbar_init(&drained, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -178,6 +191,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_s;
     volatile int* abortp = &abort_flag;
+    int tma_issued = 0;        // thread 0 only: k-steps whose two copies were started
 
     if (warp == 0) {
         // ---------------- TMA producer
@@ -193,6 +207,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 else if (WF == WF_MXFP4) tma_load_2d(q_s(s), &wmap, k / 2, wrow0 + n0, &full[s]);     // two weights per byte
                 else tma_load_2d(a_s(s), &wmap, k, wrow0 + n0, &full[s]);                              // bf16, 128-byte swizzle
                 tma_load_2d(x_s(s), &xmap, k, m0, &full[s]);
+                tma_issued = it + 1;
             }
         }
     } else if (warp == 1) {
@@ -326,14 +341,32 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             }
         }
     }
-    if (abort_flag && threadIdx.x == 0) {
-        atomicOr(p.err, 0x1000);
-        // a wait ran out: give copies that are still in flight time to land before this CTA's shared memory is released
-        const long long t_end = clock64() + 2000000;
-        while (clock64() < t_end) { }
-    }
+    // Every loop above is bounded, so all threads arrive here; from this point nothing new is issued.
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (abort_flag) {
+        // A wait ran out.  Shared memory and TMEM may only be released once everything this CTA started has landed:
+        // a late complete_tx or tcgen05.commit arrival would otherwise hit the next CTA on this SM.  So the thread that
+        // started the copies waits for the full[] phase of each of its last STAGES issues (earlier ones were waited for
+        // through empty[]), and the MMA thread commits once more to a barrier of its own, which completes when every MMA
+        // it issued (and with it every earlier commit) has.  Both waits are bounded by the global timer.
+        uint64_t t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        const uint64_t deadline = t0 + 500000000ull;             // half a second
+        bool clean = true;
+        if (threadIdx.x == 0) {
+            for (int j = max(0, tma_issued - C::STAGES); j < tma_issued; j++)
+                clean &= mbar_wait_until(&full[j % C::STAGES], (j / C::STAGES) & 1, deadline);
+            atomicOr(p.err, clean ? 0x1000 : 0x1000 | 0x4000);   // 0x4000: gave up waiting for copies in flight
+        } else if (threadIdx.x == 32) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            umma_commit(&drained);
+            clean = mbar_wait_until(&drained, 0, deadline);
+            if (!clean) atomicOr(p.err, 0x8000);                 // 0x8000: gave up waiting for tensor-core work in flight
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+    }
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");

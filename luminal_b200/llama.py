@@ -13,6 +13,10 @@ from .runtime import Context, DeviceBuffer, pack_gguf_q8_0
 
 LLAMA3_8B = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256,
                  rms_eps=1e-5, rope_theta=500000.0)
+# examples/qwen/src/model.rs:6-14 (Qwen3-4B) and examples/phi/src/model.rs:5-12 (Phi-3-mini; its head_dim of 96 is not covered
+# by the attention kernels here, which take 64 or 128)
+QWEN3_4B = dict(layers=36, hidden=2560, q_heads=32, kv_heads=8, head_dim=128, ffn=9728, vocab=151936, rms_eps=1e-6,
+                rope_theta=1000000.0, rope_mode=1, qk_norm=1, tie_head=1)
 LLAMA3_70B = dict(layers=80, hidden=8192, q_heads=64, kv_heads=8, head_dim=128, ffn=28672, vocab=128256,
                   rms_eps=1e-5, rope_theta=500000.0)
 
@@ -120,6 +124,8 @@ class Llama:
 
     def __init__(self, ctx: Context, cfg: dict, act_dtype=F32, kv_dtype=None, page_size=16, max_seqs=1, max_ctx=128,
                  kv_pages=0, embed_q8=False, tp_rank=0, tp_size=1):
+        """cfg may carry the sibling-decoder switches rope_mode (1 = half-split pairs, qwen), qk_norm and tie_head
+        (examples/qwen/src/model.rs); a phi-style model is the Llama layout with rope_theta 10000 and kv_heads = q_heads."""
         self.ctx, self.cfg = ctx, dict(cfg)
         c = LlamaCfg()
         for k in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab", "rms_eps", "rope_theta"):
@@ -128,6 +134,7 @@ class Llama:
         c.kv_dtype = act_dtype if kv_dtype is None else kv_dtype
         c.page_size, c.max_seqs, c.max_ctx, c.kv_pages = page_size, max_seqs, max_ctx, kv_pages
         c.embed_q8, c.tp_rank, c.tp_size = int(embed_q8), tp_rank, tp_size
+        c.rope_mode, c.qk_norm, c.tie_head = int(cfg.get("rope_mode", 0)), int(cfg.get("qk_norm", 0)), int(cfg.get("tie_head", 0))
         self.c = c
         h = C.c_void_p()
         ctx._check(ctx.lib.blum_llama_create(ctx.h, C.byref(c), C.byref(h)))

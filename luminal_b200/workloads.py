@@ -78,7 +78,8 @@ def tp70b(ctx: Context, comm, rank, world, steps, warmup, batch=16, prompt=1024,
         cfg["layers"] = layers
     model = Llama(ctx, cfg, act_dtype=BF16, kv_dtype=BF16, page_size=16, max_seqs=batch, max_ctx=prompt + warmup + steps + 24,
                   tp_rank=rank, tp_size=world)
-    model.set_comm(comm)
+    if world > 1:
+        model.set_comm(comm)
     model.generate_weights(seed)
     seqs, toks = [], []
     t0 = time.perf_counter()
@@ -97,12 +98,27 @@ def tp70b(ctx: Context, comm, rank, world, steps, warmup, batch=16, prompt=1024,
     ctx.timer_stop(5)
     ms = ctx.timer_ms(5)
     ctx.check_device_error()
+    # the exchanges of one step alone: 2 all-reduces per layer of [batch, hidden] bf16, back to back on the same stream
+    ar_ms = 0.0
+    if world > 1:
+        buf = ctx.alloc(batch * cfg["hidden"] * 2)
+        for timed in (False, True):
+            if timed:
+                ctx.sync()
+                ctx.timer_start(6)
+            for _ in range(2 * cfg["layers"] * (4 if timed else 1)):
+                comm.allreduce_sum(buf, batch * cfg["hidden"], BF16)
+            if timed:
+                ctx.timer_stop(6)
+                ar_ms = ctx.timer_ms(6) / 4
+        buf.free()
     out = {"metric": "tp_decode_tokens_per_s", "value": batch * steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
            "ms_per_step": ms / steps, "dtype": "bf16", "data": "synthetic", "scaling": "strong",
            "config": {"workload": "llama3-70b-shape Q8_0 TP%d, batch %d, prompt %d (seed %d)" % (world, batch, prompt, seed),
                       "layers": cfg["layers"], "allreduce": "NCCL sum, 2 per layer, %d B each" % (batch * cfg["hidden"] * 2)},
            "weight_bytes_per_gpu": model.weight_bytes,
            "achieved_weight_GBps_per_gpu": model.weight_bytes / (ms / steps) / 1e6,
+           "allreduce_ms_per_step": ar_ms, "allreduce_share": ar_ms / (ms / steps),
            "prefill": {"tokens": batch * prompt, "s": prefill_s, "tokens_per_s": batch * prompt / prefill_s}}
     model.destroy()
     return out
@@ -217,3 +233,18 @@ def sweep(ctx: Context, ms=None, shapes=None, dtype=BF16, iters=20, hbm_peak=652
             "data": "synthetic", "config": {"workload": "Q8_0 matmul operator sweep (seed 1), bf16 in / f32 accumulate / bf16 out",
                                               "l2": "launches rotate through weight copies larger than L2"},
             "peaks": {"hbm_GBps": hbm_peak, "bf16_TFLOPs_burst": tc_peak}, "rows": rows}
+
+
+def tp_parity(ctx: Context, comm, rank, world, golden_npz):
+    """A small decoder that every tensor-parallel degree of one node divides, sharded over `world` ranks, seeded weights from
+    the library's own generator, f32: its 8 greedy ids against the CPU oracle's (stored in the golden fixture)."""
+    cfg = dict(layers=2, hidden=512, q_heads=8, kv_heads=8, head_dim=64, ffn=1024, vocab=512, rms_eps=1e-5, rope_theta=500000.0)
+    model = Llama(ctx, cfg, act_dtype=F32, page_size=4, max_seqs=1, max_ctx=32, tp_rank=rank, tp_size=world)
+    if world > 1:
+        model.set_comm(comm)
+    model.generate_weights(0)
+    got = model.greedy(gen_token_ids(0, 1, 6, cfg["vocab"]), 8)
+    ctx.check_device_error()
+    model.destroy()
+    want = np.load(golden_npz)["tp_greedy_ids_f32"].tolist()
+    return {"ids": [int(t) for t in got], "golden": want, "identical": [int(t) for t in got] == want, "tp": world}

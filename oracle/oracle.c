@@ -225,6 +225,24 @@ void orc_rope(float* x, const int32_t* positions, int64_t T, int heads, int head
             }
 }
 
+/* Half-split RoPE of the qwen decoder (examples/qwen/src/model.rs:52-77): freqs = [f, f], rotated = [-x[d/2:], x[:d/2]],
+ * out = x * cos(freqs) + rotated * sin(freqs); so pair (x[i], x[i + d/2]) is rotated by pos * f_i. */
+void orc_rope_half(float* x, const int32_t* positions, int64_t T, int heads, int head_dim, float theta) {
+    float inv_freq[256];
+    orc_rope_inv_freq(theta, head_dim, inv_freq);
+    const int h2 = head_dim / 2;
+    for (int64_t t = 0; t < T; t++)
+        for (int h = 0; h < heads; h++)
+            for (int i = 0; i < h2; i++) {
+                const float a = (float)positions[t] * inv_freq[i];
+                const float sn = sinf(a), cs = sinf(1.5707964f - a);
+                float* p = x + (t * heads + h) * head_dim;
+                const float x0 = p[i], x1 = p[i + h2];
+                p[i] = x0 * cs - x1 * sn;
+                p[i + h2] = x1 * cs + x0 * sn;
+            }
+}
+
 /* triu(size, diagonal): 1 where col - row >= diagonal (src/hl_ops/other.rs:103-109). */
 void orc_triu(int size, int diagonal, float* out) {
     for (int r = 0; r < size; r++) for (int c = 0; c < size; c++) out[r * size + c] = (c - r >= diagonal) ? 1.0f : 0.0f;
@@ -287,6 +305,13 @@ typedef struct orc_llama {
     float** vcache;
     int64_t ctx_cap;
     int32_t round_mode;                 /* 0: f32 activations; 2: round activations to bf16 after every op */
+    /* sibling decoders (all zero / NULL = Llama): examples/qwen/src/model.rs, examples/phi/src/model.rs */
+    int32_t rope_mode;                  /* 0 interleaved pairs, 1 half-split pairs */
+    int32_t qk_norm;                    /* per-head RMSNorm with weight on q and k before RoPE (qwen model.rs:93-105) */
+    int32_t tie_head;                   /* logits = x . embedding^T (qwen model.rs:233) */
+    const float** q_norm;               /* per layer [head_dim] */
+    const float** k_norm;
+    orc_q8 embed_q8;                    /* Q8_0 embedding table (q == NULL: the f32 table `embed` is used) */
 } orc_llama;
 
 static void act_round(const orc_llama* m, float* a, int64_t n) { if (m->round_mode == 2) orc_round_bf16(a, n); else if (m->round_mode == 1) orc_round_f16(a, n); }
@@ -303,13 +328,25 @@ int orc_llama_forward(const orc_llama* m, const int32_t* ids, int64_t T, int64_t
     float* gt = (float*)malloc((size_t)T * F * 4), *up = (float*)malloc((size_t)T * F * 4);
     int32_t* pos = (int32_t*)malloc((size_t)T * 4);
     if (!x || !r || !qb || !kb || !vb || !ao || !y || !gt || !up || !pos) return -1;
-    for (int64_t t = 0; t < T; t++) { pos[t] = (int32_t)(p + t); memcpy(x + t * H, m->embed + (int64_t)ids[t] * H, (size_t)H * 4); }
+    for (int64_t t = 0; t < T; t++) {
+        pos[t] = (int32_t)(p + t);
+        if (m->embed_q8.q) {           /* w = (float)q * d, row ids[t] (crates/luminal_cuda/src/quantized.rs:202-233) */
+            const int8_t* qr = m->embed_q8.q + (int64_t)ids[t] * H;
+            const uint16_t* dr = m->embed_q8.d + (int64_t)ids[t] * (H / 32);
+            for (int k = 0; k < H; k++) x[t * H + k] = (float)qr[k] * orc_f16_to_f32(dr[k / 32]);
+        } else memcpy(x + t * H, m->embed + (int64_t)ids[t] * H, (size_t)H * 4);
+    }
     act_round(m, x, T * H);
     for (int l = 0; l < m->layers; l++) {
         orc_rmsnorm(x, m->attn_norm[l], m->eps, T, H, r); act_round(m, r, T * H);
         linear(&m->wq[l], r, T, qb); linear(&m->wk[l], r, T, kb); linear(&m->wv[l], r, T, vb);
         act_round(m, qb, T * nq * d); act_round(m, kb, T * nkv * d); act_round(m, vb, T * nkv * d);
-        orc_rope(qb, pos, T, nq, d, m->theta); orc_rope(kb, pos, T, nkv, d, m->theta);
+        if (m->qk_norm) {              /* LayerNorm(head_dim, weight, no bias, no mean) over every head */
+            orc_rmsnorm(qb, m->q_norm[l], m->eps, T * nq, d, qb); orc_rmsnorm(kb, m->k_norm[l], m->eps, T * nkv, d, kb);
+            act_round(m, qb, T * nq * d); act_round(m, kb, T * nkv * d);
+        }
+        if (m->rope_mode == 1) { orc_rope_half(qb, pos, T, nq, d, m->theta); orc_rope_half(kb, pos, T, nkv, d, m->theta); }
+        else { orc_rope(qb, pos, T, nq, d, m->theta); orc_rope(kb, pos, T, nkv, d, m->theta); }
         act_round(m, qb, T * nq * d); act_round(m, kb, T * nkv * d);
         for (int64_t t = 0; t < T; t++)
             for (int h = 0; h < nkv; h++) {
@@ -328,7 +365,7 @@ int orc_llama_forward(const orc_llama* m, const int32_t* ids, int64_t T, int64_t
         act_round(m, x, T * H);
     }
     orc_rmsnorm(x + (T - 1) * H, m->out_norm, m->eps, 1, H, r); act_round(m, r, H);
-    linear(&m->head, r, 1, logits);
+    linear(m->tie_head ? &m->embed_q8 : &m->head, r, 1, logits);
     free(x); free(r); free(qb); free(kb); free(vb); free(ao); free(y); free(gt); free(up); free(pos);
     return 0;
 }

@@ -222,6 +222,8 @@ class _Llama(C.Structure):
         ("wgate", C.POINTER(_Q8)), ("wup", C.POINTER(_Q8)), ("wdown", C.POINTER(_Q8)),
         ("kcache", C.POINTER(C.c_void_p)), ("vcache", C.POINTER(C.c_void_p)),
         ("ctx_cap", C.c_int64), ("round_mode", C.c_int32),
+        ("rope_mode", C.c_int32), ("qk_norm", C.c_int32), ("tie_head", C.c_int32),
+        ("q_norm", C.POINTER(C.c_void_p)), ("k_norm", C.POINTER(C.c_void_p)), ("embed_q8", _Q8),
     ]
 
 
@@ -253,7 +255,18 @@ class Llama:
             self.keep += [q, d]
             return _Q8(q.ctypes.data, d.ctypes.data, q.shape[0], q.shape[1])
 
-        m.embed, m.out_norm, m.head = f32("token_embd.weight"), f32("output_norm.weight"), q8("output.weight")
+        m.rope_mode, m.qk_norm, m.tie_head = int(cfg.get("rope_mode", 0)), int(cfg.get("qk_norm", 0)), int(cfg.get("tie_head", 0))
+        m.out_norm = f32("output_norm.weight")
+        if isinstance(weights["token_embd.weight"], tuple):
+            m.embed_q8 = q8("token_embd.weight")           # Q8_0 embedding table (QuantizedGather)
+        else:
+            m.embed = f32("token_embd.weight")
+        if not m.tie_head:
+            m.head = q8("output.weight")
+        if m.qk_norm:
+            self.q_norm = (C.c_void_p * L)(*[f32("blk.%d.attn_q_norm.weight" % i) for i in range(L)])
+            self.k_norm = (C.c_void_p * L)(*[f32("blk.%d.attn_k_norm.weight" % i) for i in range(L)])
+            m.q_norm, m.k_norm = self.q_norm, self.k_norm
         self.attn_norm = (C.c_void_p * L)(*[f32("blk.%d.attn_norm.weight" % i) for i in range(L)])
         self.ffn_norm = (C.c_void_p * L)(*[f32("blk.%d.ffn_norm.weight" % i) for i in range(L)])
         m.attn_norm, m.ffn_norm = self.attn_norm, self.ffn_norm

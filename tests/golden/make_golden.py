@@ -17,7 +17,7 @@ for p in (ROOT, os.path.dirname(HERE)):
     if p not in sys.path:
         sys.path.insert(0, p)
 
-from helpers import TINY_CFG, make_weights  # noqa: E402
+from helpers import TINY_CFG, TP_CFG, make_weights  # noqa: E402
 
 Q8_CASES = [(64, 256, 1), (96, 512, 3), (40, 1024, 8)]   # (N, K, M); tensor id 100+i, activations id 200+i, seed 1
 
@@ -56,6 +56,14 @@ def compute(orc):
         logits = model.forward([tok])
     out["llama_greedy_ids"] = np.array(toks, np.int32)
     out["llama_last_logits"] = logits.copy()
+    # a decoder every tensor-parallel degree of one node divides (seed 0; prompt ids tensor id 1): 6-token prompt, 8 greedy steps,
+    # bf16 activations as the tensor-parallel configuration runs them
+    w = make_weights(orc, TP_CFG, seed=0)
+    for key, mode in (("tp_greedy_ids_f32", 0), ("tp_greedy_ids_bf16", 2)):
+        model = orc.Llama(TP_CFG, w, ctx_cap=32, round_mode=mode)
+        ids, gaps = model.greedy(orc.gen_token_ids(0, 1, 6, TP_CFG["vocab"]), 8)
+        out[key] = np.array(ids, np.int32)
+        out[key.replace("ids", "gaps")] = np.array(gaps, np.float32)
     return out
 
 

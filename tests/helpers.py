@@ -19,7 +19,7 @@ def assert_parity(got, want, max_abs=MAX_ABS, rel=REL, what=""):
     return err
 
 
-from oracle.weights import LLAMA8B_CFG, TINY_CFG, fnv1a, make_weights, tensor_shapes  # noqa: F401  (re-exported)
+from oracle.weights import LLAMA8B_CFG, TINY_CFG, TP_CFG, TINY_PHI_CFG, TINY_QWEN_CFG, fnv1a, make_weights, tensor_shapes  # noqa: F401  (re-exported)
 
 
 def f16_bits_to_f64(bits):
@@ -48,8 +48,13 @@ class NumpyLlama:
         d = self.cfg["head_dim"]
         inv = 1.0 / self.cfg["rope_theta"] ** (np.arange(d // 2) * 2.0 / d)
         a = pos[:, None, None] * inv[None, None, :]
-        x0, x1 = x[..., 0::2], x[..., 1::2]
         out = np.empty_like(x)
+        if self.cfg.get("rope_mode", 0) == 1:          # half-split pairs (x[i], x[i + d/2]): examples/qwen/src/model.rs:52-77
+            x0, x1 = x[..., :d // 2], x[..., d // 2:]
+            out[..., :d // 2] = x0 * np.cos(a) - x1 * np.sin(a)
+            out[..., d // 2:] = x1 * np.cos(a) + x0 * np.sin(a)
+            return out
+        x0, x1 = x[..., 0::2], x[..., 1::2]
         out[..., 0::2] = x0 * np.cos(a) - x1 * np.sin(a)
         out[..., 1::2] = x0 * np.sin(a) + x1 * np.cos(a)
         return out
@@ -59,13 +64,17 @@ class NumpyLlama:
         T, nq, nkv, d = len(ids), c["q_heads"], c["kv_heads"], c["head_dim"]
         p = self.k[0].shape[1]
         pos = np.arange(p, p + T, dtype=np.float64)
-        x = self.w["token_embd.weight"][np.asarray(ids)].astype(np.float64)
+        emb = self.deq["token_embd.weight"] if "token_embd.weight" in self.deq else self.w["token_embd.weight"]
+        x = emb[np.asarray(ids)].astype(np.float64)
         for l in range(c["layers"]):
             pre = "blk.%d." % l
             r = self._norm(x, self.w[pre + "attn_norm.weight"])
             q = (r @ self.deq[pre + "attn_q.weight"].T).reshape(T, nq, d)
             k = (r @ self.deq[pre + "attn_k.weight"].T).reshape(T, nkv, d)
             v = (r @ self.deq[pre + "attn_v.weight"].T).reshape(T, nkv, d)
+            if c.get("qk_norm"):
+                q = self._norm(q, self.w[pre + "attn_q_norm.weight"])
+                k = self._norm(k, self.w[pre + "attn_k_norm.weight"])
             q, k = self._rope(q, pos), self._rope(k, pos)
             self.k[l] = np.concatenate([self.k[l], k.transpose(1, 0, 2)], axis=1)
             self.v[l] = np.concatenate([self.v[l], v.transpose(1, 0, 2)], axis=1)
@@ -83,4 +92,5 @@ class NumpyLlama:
             u = r @ self.deq[pre + "ffn_up.weight"].T
             x = x + (u * (g / (1.0 + np.exp(-g)))) @ self.deq[pre + "ffn_down.weight"].T
         r = self._norm(x[-1:], self.w["output_norm.weight"])
-        return (r @ self.deq["output.weight"].T)[0]
+        head = self.deq["token_embd.weight"] if c.get("tie_head") else self.deq["output.weight"]
+        return (r @ head.T)[0]

@@ -4,7 +4,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import LLAMA8B_CFG, TINY_CFG, assert_parity, make_weights
+from helpers import LLAMA8B_CFG, TINY_CFG, TINY_PHI_CFG, TINY_QWEN_CFG, assert_parity, make_weights
 from luminal_b200 import BF16, F32, BlumError, runtime
 from luminal_b200.llama import Llama
 
@@ -211,6 +211,42 @@ def test_a_second_larger_model_leaves_the_first_models_captured_step_valid(ctx, 
     ctx.check_device_error()
     b.destroy()
     a.destroy()
+
+
+@pytest.mark.parametrize("cfg", [TINY_QWEN_CFG, TINY_PHI_CFG], ids=["qwen", "phi"])
+def test_sibling_decoders_match_the_oracle(ctx, orc, cfg):
+    """qwen (half-split rotary pairs, per-head q/k norm, tied head over a Q8_0 embedding table) and phi (theta 1e4, as
+    many kv heads as q heads) on the same kernels: prompt pass, single-sequence decode and a 5-row batch against the
+    oracle, f32 activations."""
+    w = make_weights(orc, cfg, seed=9, norm_random=True)
+    m = Llama(ctx, cfg, act_dtype=F32, page_size=4, max_seqs=6, max_ctx=64, embed_q8=bool(cfg.get("embed_q8")))
+    m.load_weights(w)
+    ref = orc.Llama(cfg, w, ctx_cap=64)
+    prompt = orc.gen_token_ids(9, 1, 7, cfg["vocab"])
+    seq = m.new_sequence()
+    tok, logits = m.prefill(seq, prompt, want_logits=True)
+    want = ref.forward(prompt)
+    assert_parity(logits, want, max_abs=1e-3, rel=1e-3, what="sibling prefill logits")
+    ids = [tok]
+    for step in range(6):
+        assert tok == orc.argmax(want)
+        out, lg = m.decode([seq], [tok], want_logits=True)
+        want = ref.forward([tok])
+        assert_parity(lg[0], want, max_abs=1e-3, rel=1e-3, what="sibling decode logits, step %d" % step)
+        tok = int(out[0])
+        ids.append(tok)
+    m.kv.seq_free(seq)
+    # the same tokens come out of a 5-row batch (rows 1..4 are other prompts): the batched path applies the same glue
+    prompts = [prompt] + [orc.gen_token_ids(9, 20 + i, 3 + i, cfg["vocab"]) for i in range(4)]
+    seqs = [m.new_sequence() for _ in prompts]
+    toks = [[m.prefill(s, p)] for s, p in zip(seqs, prompts)]
+    for _ in range(6):
+        out = m.decode(seqs, [t[-1] for t in toks])
+        for t, o in zip(toks, out):
+            t.append(int(o))
+    assert toks[0] == ids
+    ctx.check_device_error()
+    m.destroy()
 
 
 def test_model_error_paths(ctx, tiny):

@@ -6,7 +6,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import TINY_CFG, NumpyLlama, assert_parity, f16_bits_to_f64, make_weights
+from helpers import TINY_CFG, TINY_PHI_CFG, TINY_QWEN_CFG, NumpyLlama, assert_parity, f16_bits_to_f64, make_weights
 
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
@@ -163,6 +163,24 @@ def test_llama_oracle_against_float64_model(orc):
     c_model = orc.Llama(cfg, w, ctx_cap=16)
     n_model = NumpyLlama(cfg, w)
     ids = orc.gen_token_ids(7, 1, 5, cfg["vocab"])
+    a, b = c_model.forward(ids), n_model.forward(ids)
+    assert_parity(a, b, max_abs=1e-4, rel=1e-4, what="prefill logits")
+    for _ in range(3):
+        tok = orc.argmax(a)
+        assert tok == int(np.argmax(b))
+        a, b = c_model.forward([tok]), n_model.forward([tok])
+        assert_parity(a, b, max_abs=1e-4, rel=1e-4, what="decode logits")
+
+
+@pytest.mark.parametrize("cfg", [TINY_QWEN_CFG, TINY_PHI_CFG], ids=["qwen", "phi"])
+def test_sibling_decoders_against_float64_model(orc, cfg):
+    """The qwen form (half-split rotary pairs, per-head q/k RMSNorm, tied head over a Q8_0 embedding table:
+    examples/qwen/src/model.rs:52-105,233) and the phi form (interleaved pairs, theta 1e4, one kv head per q head:
+    examples/phi/src/model.rs:50-70) of the C oracle against the independent float64 model."""
+    w = make_weights(orc, cfg, seed=9, norm_random=True)
+    c_model = orc.Llama(cfg, w, ctx_cap=16)
+    n_model = NumpyLlama(cfg, w)
+    ids = orc.gen_token_ids(9, 1, 5, cfg["vocab"])
     a, b = c_model.forward(ids), n_model.forward(ids)
     assert_parity(a, b, max_abs=1e-4, rel=1e-4, what="prefill logits")
     for _ in range(3):
