@@ -146,7 +146,7 @@ def run_reference(args, rank):
 
 
 # ------------------------------------------------------------------ own arm
-def kernel_table(ctx, model, lib, hbm_peak):
+def kernel_table(ctx, model, lib, hbm_peak, layers):
     """Per-kernel achieved HBM bandwidth of the operator-level Q8_0 GEMV entry points on this model's matrices.  Each row
     captures one launch per layer (32 different matrices: 0.6 to 4 GB per pass, so no launch finds its weights in L2) in a
     CUDA graph and times replays of it with CUDA events, so the figures are device time, not host launch time."""
@@ -178,7 +178,7 @@ def kernel_table(ctx, model, lib, hbm_peak):
         rows[name] = {"launches_per_step": count if count > 1 else 1, "us": ms * 1e3, "bytes": bytes_per_launch,
                       "GBps": bytes_per_launch / ms / 1e6, "frac_of_peak": bytes_per_launch / ms / 1e6 / hbm_peak}
 
-    L = CFG["layers"]
+    L = layers
     W = lambda l, which: lib.blum_llama_layer_weight(model.h, l, which)
     NW = lambda l, which: lib.blum_llama_norm_weight(model.h, l, which)
     qkv_rows = (CFG["q_heads"] + 2 * CFG["kv_heads"]) * CFG["head_dim"]
@@ -216,8 +216,8 @@ def tp_leg(ctx, rank, world, dist):
         comm = Comm(ctx, world, rank, bytes(uid.cpu().numpy().tobytes()), init_timeout_ms=60000)
     out = {"tp_parity": workloads.tp_parity(ctx, comm, rank, world, os.path.join(ROOT, "tests", "golden", "oracle_vectors.npz"))}
     rec = workloads.tp70b(ctx, comm, rank, world, steps=8, warmup=3)
-    keep = ("value", "unit", "ms_per_step", "steps", "weight_bytes_per_gpu", "achieved_weight_GBps_per_gpu", "allreduce_ms_per_step",
-            "allreduce_share", "prefill", "config", "dtype")
+    keep = ("value", "unit", "ms_per_step", "steps", "weight_bytes_per_gpu", "achieved_weight_GBps_per_gpu", "ms_per_step_nccl",
+            "nccl_exchange_ms_per_step", "nccl_exchange_share", "peer_exchange_ms_per_step", "peer_exchange_share", "prefill", "config", "dtype")
     out["tp70b"] = {k: rec[k] for k in keep if k in rec}
     out["tp70b"]["tp"] = world
     if comm is not None:
@@ -252,7 +252,8 @@ def run_own(args, rank, world, local_rank):
     ctx = Context(local_rank)
     lib = ctx.lib
     max_ctx = PROMPT_LEN + 2 * (args.warmup + args.steps) + 8
-    model = Llama(ctx, CFG, act_dtype=F32, page_size=16, max_seqs=1, max_ctx=max_ctx)
+    cfg = dict(CFG, layers=args.layers) if args.layers else CFG      # --layers: a truncated model for profiler captures only
+    model = Llama(ctx, cfg, act_dtype=F32, page_size=16, max_seqs=1, max_ctx=max_ctx)
     model.generate_weights(SEED)
     prompt = gen_token_ids(SEED, 1 + rank, PROMPT_LEN, CFG["vocab"])
     hbm_peak, peak_kind = measured_peaks()
@@ -306,7 +307,7 @@ def run_own(args, rank, world, local_rank):
     ms_e2e = max_over_ranks(ms_e2e)
     ctx.check_device_error()
 
-    ktab = kernel_table(ctx, model, lib, hbm_peak) if rank == 0 else None
+    ktab = kernel_table(ctx, model, lib, hbm_peak, cfg["layers"]) if rank == 0 else None
     wbytes = model.weight_bytes
     model.destroy()
     # ---- tensor parallelism over the same N GPUs (the 70B configuration) and its parity check: every rank takes part
@@ -324,11 +325,11 @@ def run_own(args, rank, world, local_rank):
     tok_s = world * args.steps / (ms_dev / 1e3)
     # algorithmic bytes of one launch of the persistent decode kernel: every Q8_0 weight once, the norm weights, the
     # embedding row, and the cached K/V rows of the context (f32) read plus the new row written
-    kv_bytes = CFG["layers"] * 2 * CFG["kv_heads"] * CFG["head_dim"] * 4 * (ctx_at_timing + 1)
-    stream_bytes = wbytes + (2 * CFG["layers"] + 1) * CFG["hidden"] * 4 + CFG["hidden"] * 4 + kv_bytes
+    kv_bytes = cfg["layers"] * 2 * cfg["kv_heads"] * cfg["head_dim"] * 4 * (ctx_at_timing + 1)
+    stream_bytes = wbytes + (2 * cfg["layers"] + 1) * cfg["hidden"] * 4 + cfg["hidden"] * 4 + kv_bytes
     if stream_us is not None:
         gbps = stream_bytes / (stream_us * 1e-6) / 1e9
-        roof = {"bound": "hbm", "kernel": "decode_stream_kernel (the whole single-sequence step: 161 phases, one launch)",
+        roof = {"bound": "hbm", "kernel": "decode_stream_kernel (the whole single-sequence step: %d phases, one launch)" % (5 * cfg["layers"] + 1),
                 "achieved": gbps, "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbps / hbm_peak,
                 "launch_us": stream_us, "algorithmic_bytes": stream_bytes,
                 # DRAM read + write of one launch, scaled by layer count from an ncu capture of a 4-layer model of the same widths
@@ -361,6 +362,8 @@ def run_own(args, rank, world, local_rank):
         # the operator-level GEMV entry points on the same matrices (what a luminal operator would call one by one)
         "kernels": ktab,
     }
+    if args.layers:
+        line["config"]["truncated"] = "%d layers instead of %d: a profiler case, not a bench value" % (cfg["layers"], CFG["layers"])
     if tp is not None:
         line["tp70b"] = tp.get("tp70b", tp)
         line["tp_parity"] = tp.get("tp_parity")
@@ -437,7 +440,7 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel 70B record and its parity check")
     ap.add_argument("--workload", default="decode8b", choices=["decode8b", "serve64", "tp70b", "moe", "moe_ep", "sweep"],
                     help="decode8b (default, the headline metric) or one of the secondary configurations")
-    ap.add_argument("--layers", type=int, default=None, help="secondary workloads only: truncate the model to this many layers")
+    ap.add_argument("--layers", type=int, default=None, help="truncate the model to this many layers (small cases for profiler captures; the line says so)")
     ap.add_argument("--prompt", type=int, default=None, help="tp70b only: prompt length (default 1024)")
     ap.add_argument("--m", default=None, help="sweep only: comma-separated row counts (default 1,8,64,512,4096)")
     args = ap.parse_args()

@@ -45,6 +45,7 @@ typedef struct blum_q8_weight blum_q8_weight;
 typedef struct blum_kv blum_kv;
 typedef struct blum_llama blum_llama;
 typedef struct blum_comm blum_comm;
+typedef struct blum_peer blum_peer;
 
 /* ------------------------------------------------------------------ lifecycle */
 
@@ -295,6 +296,25 @@ int blum_alltoallv(blum_ctx* ctx, blum_comm* comm, const void* send, const int64
                    const int64_t* send_offsets, void* recv, const int64_t* recv_bytes, const int64_t* recv_offsets,
                    int timeout_ms);
 
+/* Row-parallel exchange without a library collective (no counterpart in the reference; the unsharded computation is the
+ * o_proj / down_proj matmul, the residual add of examples/llama/src/model.rs:180,186 and the RMSNorm of
+ * crates/luminal_nn/src/norm.rs:62-65).  blum_peer_create is collective over `comm`: every rank allocates an exchange
+ * area of two slots of max_rows rows of row_bytes, exports it with a CUDA IPC handle and maps every peer's (one process
+ * per GPU with peer access; any failure on any rank fails the call on every rank with BLUM_ERR_COMM and nothing is left
+ * mapped).  A projection kernel writes its partial product [rows][dim] into blum_peer_slot(peer, slot); then
+ * blum_allreduce_fused, ONE kernel with one CTA per row, announces the row to every peer, waits for theirs (bounded to one
+ * second: on expiry bit 0x10000 of the device error word is set and the call's results are undefined, the context stays
+ * usable), loads the row of every rank with plain peer loads over NVLink, sums in rank order in f32 (so every rank gets
+ * identical bits), rounds to `dtype`, adds the residual row x into x_out (x_out may be x) and, when xn_out is given, writes
+ * rmsnorm(x_out) * norm_w there.  Consecutive calls must alternate slot 0 and 1 on every rank (BLUM_ERR_STATE otherwise):
+ * that is what makes a slot safe to overwrite two exchanges later.  Row counts above max_rows are for NCCL. */
+int blum_peer_create(blum_ctx* ctx, blum_comm* comm, int64_t row_bytes, int max_rows, int timeout_ms, blum_peer** out);
+int blum_peer_destroy(blum_ctx* ctx, blum_peer* peer);
+void* blum_peer_slot(blum_peer* peer, int slot);
+int blum_peer_max_rows(const blum_peer* peer);
+int blum_allreduce_fused(blum_ctx* ctx, blum_peer* peer, int slot, const void* x, const float* norm_w, float eps,
+                         void* xn_out, void* x_out, blum_dtype dtype, int rows, int64_t dim);
+
 /* ------------------------------------------------------------------ Llama decoder
  * The model of examples/llama/src/model.rs as one object: weights, KV pool, scratch and a
  * captured CUDA graph of the single-token step (the reference executes ~10^3 nodes per token
@@ -326,6 +346,11 @@ int blum_llama_set_tensor(blum_ctx* ctx, blum_llama* m, const char* gguf_name, c
                           size_t nbytes, int is_q8_0);
 uint64_t blum_llama_tensor_id(const char* gguf_name);
 int blum_llama_set_comm(blum_ctx* ctx, blum_llama* m, blum_comm* comm);
+/* Tensor-parallel models only (no counterpart in the reference): enable = 1 makes steps of up to 64 rows sum their
+ * row-parallel projections with blum_allreduce_fused over a peer-mapped area (collective: every rank must call it);
+ * enable = 0 returns to NCCL all-reduce + add.  Larger row counts always use NCCL. */
+int blum_llama_set_peer_allreduce(blum_ctx* ctx, blum_llama* m, int enable, int timeout_ms);
+int blum_llama_peer_allreduce(const blum_llama* m);
 blum_kv* blum_llama_kv(blum_llama* m);
 /* Prefill `T` prompt tokens (host int32 ids) of sequence `seq` starting at its current length;
  * returns the greedy next token.  logits_out (host f32 [vocab]) may be NULL. */

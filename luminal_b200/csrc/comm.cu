@@ -84,6 +84,7 @@ struct blum_comm {
     ncclComm_t comm = nullptr;
     int rank = 0, size = 1;
     bool aborted = false;            // a watchdog gave up on this communicator: every later call fails at once
+    bool nonblocking = false;        // initialised with blocking = 0: calls may answer ncclInProgress and are then polled
 };
 
 #define BLUM_NCCL(ctx, call)                                                                                   \
@@ -97,6 +98,33 @@ struct blum_comm {
     do {                                                                                                       \
         if ((c)->aborted || !(c)->comm)                                                                        \
             return blum_fail((ctx), BLUM_ERR_COMM, "%s: the communicator was aborted after an earlier timeout or error", what); \
+    } while (0)
+
+// A communicator that was initialised without blocking answers ncclInProgress from any call that has not finished its
+// host-side work; the call's real status is then read from ncclCommGetAsyncError.  Bounded: a stuck call aborts the
+// communicator like the watchdog does.
+#define COMM_SETTLE_MS 60000.0
+static double now_ms();
+static void nap();
+static void comm_abort(NcclApi* nccl, blum_comm* c);
+static ncclResult_t comm_settle(NcclApi* nccl, blum_comm* c, ncclResult_t r) {
+    if (r != ncclInProgress || !c->nonblocking || !nccl->CommGetAsyncError) return r;
+    const double t0 = now_ms();
+    for (;;) {
+        ncclResult_t st = ncclSuccess;
+        if (nccl->CommGetAsyncError(c->comm, &st) != ncclSuccess) return ncclInternalError;
+        if (st != ncclInProgress) return st;
+        const double waited = now_ms() - t0;
+        if (waited > COMM_SETTLE_MS) { comm_abort(nccl, c); return ncclInternalError; }
+        if (waited > 2.0) nap();          // the usual case settles within microseconds: poll, do not sleep
+    }
+}
+#define BLUM_NCCL_ON(ctx, c, call)                                                                             \
+    do {                                                                                                       \
+        ncclResult_t r__ = comm_settle(nccl, (c), (call));                                                     \
+        if (r__ != ncclSuccess)                                                                                \
+            return blum_fail((ctx), BLUM_ERR_COMM, "%s failed: %s (%s:%d)", #call, nccl->GetErrorString(r__),    \
+                             __FILE__, __LINE__);                                                              \
     } while (0)
 
 static ncclDataType_t nccl_dtype(int dt) { return dt == BLUM_F32 ? ncclFloat32 : dt == BLUM_F16 ? ncclFloat16 : ncclBfloat16; }
@@ -174,6 +202,7 @@ int blum_comm_init_rank(blum_ctx* ctx, int nranks, int rank, const void* id_128_
         // non-blocking init: a rank that never joins must not hold this one for ever
         ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
         cfg.blocking = 0;
+        c->nonblocking = true;
         r = nccl->CommInitRankConfig(&c->comm, nranks, id, rank, &cfg);
         const double t0 = now_ms();
         while (r == ncclInProgress || (r == ncclSuccess && c->comm)) {
@@ -220,7 +249,7 @@ int blum_allreduce_sum(blum_ctx* ctx, blum_comm* c, void* buf, int64_t count, bl
     if (count == 0 || c->size == 1) return BLUM_OK;
     NCCL_API_OR_FAIL(ctx);
     COMM_USABLE(ctx, c, "allreduce");
-    BLUM_NCCL(ctx, nccl->AllReduce(buf, buf, (size_t)count, nccl_dtype(dtype), ncclSum, c->comm, ctx->stream));
+    BLUM_NCCL_ON(ctx, c, nccl->AllReduce(buf, buf, (size_t)count, nccl_dtype(dtype), ncclSum, c->comm, ctx->stream));
     return comm_watch(ctx, nccl, c, timeout_ms, "allreduce");
 }
 
@@ -231,7 +260,7 @@ int blum_allgather(blum_ctx* ctx, blum_comm* c, const void* send, void* recv, in
     if (bytes_per_rank == 0) return BLUM_OK;
     NCCL_API_OR_FAIL(ctx);
     COMM_USABLE(ctx, c, "allgather");
-    BLUM_NCCL(ctx, nccl->AllGather(send, recv, (size_t)bytes_per_rank, ncclInt8, c->comm, ctx->stream));
+    BLUM_NCCL_ON(ctx, c, nccl->AllGather(send, recv, (size_t)bytes_per_rank, ncclInt8, c->comm, ctx->stream));
     return comm_watch(ctx, nccl, c, timeout_ms, "allgather");
 }
 
@@ -247,14 +276,14 @@ int blum_alltoallv(blum_ctx* ctx, blum_comm* c, const void* send, const int64_t*
     for (int p = 0; p < c->size; p++) {
         if (send_bytes[p] > 0) {
             ncclResult_t r = nccl->Send((const char*)send + send_offsets[p], (size_t)send_bytes[p], ncclInt8, p, c->comm, ctx->stream);
-            if (r != ncclSuccess) { nccl->GroupEnd(); return blum_fail(ctx, BLUM_ERR_COMM, "ncclSend to %d failed: %s", p, nccl->GetErrorString(r)); }
+            if (r != ncclSuccess && r != ncclInProgress) { nccl->GroupEnd(); return blum_fail(ctx, BLUM_ERR_COMM, "ncclSend to %d failed: %s", p, nccl->GetErrorString(r)); }
         }
         if (recv_bytes[p] > 0) {
             ncclResult_t r = nccl->Recv((char*)recv + recv_offsets[p], (size_t)recv_bytes[p], ncclInt8, p, c->comm, ctx->stream);
-            if (r != ncclSuccess) { nccl->GroupEnd(); return blum_fail(ctx, BLUM_ERR_COMM, "ncclRecv from %d failed: %s", p, nccl->GetErrorString(r)); }
+            if (r != ncclSuccess && r != ncclInProgress) { nccl->GroupEnd(); return blum_fail(ctx, BLUM_ERR_COMM, "ncclRecv from %d failed: %s", p, nccl->GetErrorString(r)); }
         }
     }
-    BLUM_NCCL(ctx, nccl->GroupEnd());
+    BLUM_NCCL_ON(ctx, c, nccl->GroupEnd());
     return comm_watch(ctx, nccl, c, timeout_ms, "alltoallv");
 }
 

@@ -37,6 +37,7 @@ struct StreamPlan {
     uint64_t weights_version = 0;          // version of the model's weights the packed copy was made from
     unsigned char* packed = nullptr;
     DsPhase* d_phases = nullptr;
+    std::vector<DsPhase> h_phases;         // host copy: where each matrix's packed units start
     int nphases = 0, kmax = 0, grid = 0;
     unsigned long long* words = nullptr;   // tagged activation words: xres | qkv | attn | mid | part | attn_part
     size_t words_bytes = 0;
@@ -77,6 +78,9 @@ struct blum_llama {
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;   // (rows, nsplit) -> captured decode step
     std::map<std::pair<int, int>, int> graph_nodes;          // kernel nodes per captured step
     blum_comm* comm = nullptr;
+    void* rows_scratch = nullptr;      // digitised activations and partial sums of the prompt-chunk matmul (prefill_rows.cu)
+    size_t rows_scratch_bytes = 0;
+    blum_peer* peer = nullptr;         // peer-mapped exchange area: row-parallel sums without a library collective
     int64_t weight_bytes = 0;
 };
 
@@ -105,6 +109,22 @@ static size_t act_bytes(const blum_llama* m, int64_t elems) { return (size_t)ele
 
 #define TRY(call) do { int rc__ = (call); if (rc__) return rc__; } while (0)
 
+static bool stream_supported(blum_ctx* ctx, blum_llama* m);
+static int build_stream_plan(blum_ctx* ctx, blum_llama* m);
+
+// Rows of a prompt chunk in the f32 configuration: the projections read the stream-packed weights once per 32 rows
+// (prefill_rows.cu) instead of once per two rows through the GEMV.  Blocks of ROWS_BLOCK rows share one scratch area.
+#define ROWS_BLOCK 128
+static int rows_mm(blum_ctx* ctx, blum_llama* m, int phase, const float* x, int64_t ldx, float* y, int64_t ldy, int R, int swiglu) {
+    const DsPhase& P = m->sp.h_phases[(size_t)phase];
+    const int64_t rows_total = (int64_t)P.groups * DS_UNIT_ROWS;
+    for (int r0 = 0; r0 < R; r0 += ROWS_BLOCK) {
+        const int n = std::min(ROWS_BLOCK, R - r0);
+        TRY(blum_rows_matmul(ctx, P.w, rows_total, P.K, x + (int64_t)r0 * ldx, ldx, n, swiglu, y + (int64_t)r0 * ldy, ldy, m->rows_scratch, m->rows_scratch_bytes));
+    }
+    return BLUM_OK;
+}
+
 // ------------------------------------------------------------------ forward for R rows
 // rows are described by d_rows (ids, seq, pos, ctx); head_rows = rows whose logits are needed
 // (all for decode, the last one for prefill); everything is enqueued on ctx->stream.
@@ -116,6 +136,16 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
     if (m->embed_q8) TRY(blum_q8_0_gather(ctx, m->embed_q8, ids, R, m->x, adt));
     else TRY(blum_gather(ctx, m->embed_f32, BLUM_F32, c.vocab, H, ids, R, m->x, adt));
     const bool fused = R <= GEMV_ROWS;
+    // more rows than the GEMV takes at once, f32 activations, and the model has (or can have) the stream-packed weights
+    const bool rows_path = !fused && adt == BLUM_F32 && m->decode_path == 0 && stream_supported(ctx, m);
+    if (rows_path) {
+        if (!m->sp.built || m->sp.weights_version != m->weights_version) TRY(build_stream_plan(ctx, m));
+        if (!m->rows_scratch) {
+            const int64_t nk = std::max<int64_t>((int64_t)(H / DS_UNIT_K) * 2 * m->ffn, (int64_t)(m->ffn / DS_UNIT_K) * H);
+            m->rows_scratch_bytes = blum_rows_scratch_bytes(ROWS_BLOCK, std::max(H, m->ffn), std::max<int64_t>(nk, (int64_t)(H / DS_UNIT_K) * (m->nq + 2 * m->nkv) * d));
+            BLUM_CUDA(ctx, cudaMalloc(&m->rows_scratch, m->rows_scratch_bytes));
+        }
+    }
     // Programmatic dependent launch belongs to the fused GEMV chain, where every kernel lets its successor start early.
     // Outside it (row counts that take the GEMM kernels) the attribute buys nothing and is switched off.
     struct PdlGuard {
@@ -130,7 +160,8 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         } else {
             // (for l > 0 the previous layer's down-projection add already produced xn = rmsnorm(x) with this layer's weight)
             if (l == 0) TRY(blum_rmsnorm(ctx, m->x, nullptr, w.attn_norm, c.rms_eps, m->xn, nullptr, adt, R, H));
-            TRY(blum_q8_0_matmul(ctx, w.wqkv, m->xn, adt, m->qkv, adt, R));
+            if (rows_path) TRY(rows_mm(ctx, m, 5 * l, (const float*)m->xn, H, (float*)m->qkv, (int64_t)(m->nq + 2 * m->nkv) * d, R, 0));
+            else TRY(blum_q8_0_matmul(ctx, w.wqkv, m->xn, adt, m->qkv, adt, R));
         }
         // The sibling decoders (per-head q/k norm, half-split rotary pairs) get their glue from one extra kernel that works in
         // place on the fused rows; the kernels after it then rotate by zero angles.
@@ -154,9 +185,17 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         // summed over ranks (NCCL all-reduce) and only then added to the residual stream
         const bool tp = c.tp_size > 1;
         if (tp && !m->comm) return blum_fail(ctx, BLUM_ERR_STATE, "llama: tp_size=%d but no communicator was set (blum_llama_set_comm)", c.tp_size);
+        // with a peer-mapped exchange area and few rows, the projection writes its partial product into the area and one
+        // kernel sums over ranks, adds the residual and normalises (peer_reduce.cu); otherwise NCCL does the sum
+        const bool pull = tp && m->peer && R <= blum_peer_max_rows(m->peer);
+        void* part0 = pull ? blum_peer_slot(m->peer, 0) : nullptr;
+        void* part1 = pull ? blum_peer_slot(m->peer, 1) : nullptr;
         if (fused) {
             if (!tp) {
                 TRY(blum_gemv_dispatch(ctx, w.wo, nullptr, m->attn, adt, nullptr, 0.f, m->x, m->x, adt, R));
+            } else if (pull) {
+                TRY(blum_gemv_dispatch(ctx, w.wo, nullptr, m->attn, adt, nullptr, 0.f, nullptr, part0, adt, R));
+                TRY(blum_allreduce_fused(ctx, m->peer, 0, m->x, nullptr, 0.f, nullptr, m->x, adt, R, H));
             } else {
                 TRY(blum_gemv_dispatch(ctx, w.wo, nullptr, m->attn, adt, nullptr, 0.f, nullptr, m->xn, adt, R));
                 TRY(blum_allreduce_sum(ctx, m->comm, m->xn, (int64_t)R * H, adt, 0));
@@ -165,6 +204,9 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
             TRY(blum_gemv_dispatch(ctx, w.wgate, w.wup, m->x, adt, w.ffn_norm, c.rms_eps, nullptr, m->mid, adt, R));
             if (!tp) {
                 TRY(blum_gemv_dispatch(ctx, w.wdown, nullptr, m->mid, adt, nullptr, 0.f, m->x, m->x, adt, R));
+            } else if (pull) {
+                TRY(blum_gemv_dispatch(ctx, w.wdown, nullptr, m->mid, adt, nullptr, 0.f, nullptr, part1, adt, R));
+                TRY(blum_allreduce_fused(ctx, m->peer, 1, m->x, nullptr, 0.f, nullptr, m->x, adt, R, H));
             } else {
                 TRY(blum_gemv_dispatch(ctx, w.wdown, nullptr, m->mid, adt, nullptr, 0.f, nullptr, m->xn, adt, R));
                 TRY(blum_allreduce_sum(ctx, m->comm, m->xn, (int64_t)R * H, adt, 0));
@@ -173,16 +215,31 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         } else {
             // residual add and the following RMSNorm in one kernel: x <- x + proj (rounded as the separate add would),
             // xn <- rmsnorm(x) * weight.  The projection lands in the gate buffer, which is free here.
-            TRY(blum_q8_0_matmul(ctx, w.wo, m->attn, adt, m->gate, adt, R));
-            if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt, 0));
-            TRY(blum_rmsnorm(ctx, m->x, m->gate, w.ffn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
-            TRY(blum_q8_0_matmul(ctx, w.wgate, m->xn, adt, m->gate, adt, R));
-            TRY(blum_q8_0_matmul(ctx, w.wup, m->xn, adt, m->up, adt, R));
-            TRY(blum_swiglu(ctx, m->gate, m->up, m->mid, adt, (int64_t)R * m->ffn));
-            TRY(blum_q8_0_matmul(ctx, w.wdown, m->mid, adt, m->gate, adt, R));
-            if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt, 0));
-            if (l + 1 < c.layers) TRY(blum_rmsnorm(ctx, m->x, m->gate, m->L[l + 1].attn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
-            else TRY(blum_add(ctx, m->x, m->gate, m->x, adt, (int64_t)R * H));
+            if (rows_path) TRY(rows_mm(ctx, m, 5 * l + 2, (const float*)m->attn, (int64_t)m->nq * d, (float*)m->gate, H, R, 0));
+            else TRY(blum_q8_0_matmul(ctx, w.wo, m->attn, adt, pull ? part0 : m->gate, adt, R));
+            if (pull) {
+                TRY(blum_allreduce_fused(ctx, m->peer, 0, m->x, w.ffn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
+            } else {
+                if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt, 0));
+                TRY(blum_rmsnorm(ctx, m->x, m->gate, w.ffn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
+            }
+            if (rows_path) {
+                TRY(rows_mm(ctx, m, 5 * l + 3, (const float*)m->xn, H, (float*)m->mid, m->ffn, R, 1));       // SwiGLU in the finishing pass
+                TRY(rows_mm(ctx, m, 5 * l + 4, (const float*)m->mid, m->ffn, (float*)m->gate, H, R, 0));
+            } else {
+                TRY(blum_q8_0_matmul(ctx, w.wgate, m->xn, adt, m->gate, adt, R));
+                TRY(blum_q8_0_matmul(ctx, w.wup, m->xn, adt, m->up, adt, R));
+                TRY(blum_swiglu(ctx, m->gate, m->up, m->mid, adt, (int64_t)R * m->ffn));
+                TRY(blum_q8_0_matmul(ctx, w.wdown, m->mid, adt, pull ? part1 : m->gate, adt, R));
+            }
+            if (pull) {
+                const bool more = l + 1 < c.layers;
+                TRY(blum_allreduce_fused(ctx, m->peer, 1, m->x, more ? m->L[l + 1].attn_norm : nullptr, c.rms_eps, more ? m->xn : nullptr, m->x, adt, R, H));
+            } else {
+                if (tp) TRY(blum_allreduce_sum(ctx, m->comm, m->gate, (int64_t)R * H, adt, 0));
+                if (l + 1 < c.layers) TRY(blum_rmsnorm(ctx, m->x, m->gate, m->L[l + 1].attn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
+                else TRY(blum_add(ctx, m->x, m->gate, m->x, adt, (int64_t)R * H));
+            }
         }
     }
     // head: the reference computes logits for every position and keeps the last (examples/llama/src/main.rs:58-61);
@@ -300,6 +357,7 @@ static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
     sp.nphases = (int)ph.size();
     BLUM_CUDA(ctx, cudaMemcpyAsync(sp.d_phases, ph.data(), sizeof(DsPhase) * ph.size(), cudaMemcpyHostToDevice, ctx->stream));
     BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));      // ph is a host temporary
+    sp.h_phases = ph;
     sp.built = true;
     sp.weights_version = m->weights_version;
     return BLUM_OK;
@@ -415,6 +473,7 @@ int blum_llama_destroy(blum_ctx* ctx, blum_llama* m) {
     cudaStreamSynchronize(ctx->stream);
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
     free_stream_plan(m);
+    if (m->peer) blum_peer_destroy(ctx, m->peer);
     for (auto& w : m->L) {
         if (w.attn_norm) cudaFree(w.attn_norm);
         if (w.ffn_norm) cudaFree(w.ffn_norm);
@@ -425,7 +484,7 @@ int blum_llama_destroy(blum_ctx* ctx, blum_llama* m) {
     }
     if (!m->cfg.tie_head) blum_q8_0_weight_free(ctx, m->head);
     blum_q8_0_weight_free(ctx, m->embed_q8);
-    void* bufs[] = {m->embed_f32, m->out_norm, m->x, m->xn, m->qkv, m->q, m->attn, m->mid, m->gate, m->up, m->logits,
+    void* bufs[] = {m->rows_scratch, m->embed_f32, m->out_norm, m->x, m->xn, m->qkv, m->q, m->attn, m->mid, m->gate, m->up, m->logits,
                     m->d_rows, m->d_next, m->d_hist, m->attn_scratch, m->d_pairs};
     for (void* b : bufs) if (b) cudaFree(b);
     if (m->h_rows) cudaFreeHost(m->h_rows);
@@ -593,9 +652,31 @@ int blum_llama_stream_kernel_us(blum_ctx* ctx, blum_llama* m, int iters, float* 
 }
 int blum_llama_set_comm(blum_ctx* ctx, blum_llama* m, blum_comm* comm) {
     if (!ctx || !m) return BLUM_ERR_INVALID;
+    if (m->peer && comm != m->comm) { blum_peer_destroy(ctx, m->peer); m->peer = nullptr; }
     m->comm = comm;
     return BLUM_OK;
 }
+
+// Rows up to this count take the one-kernel exchange; larger row counts (prompt chunks) keep NCCL, whose ring / in-switch
+// algorithms move each byte once where the one-shot pull reads every peer's whole partial product.
+#define LLAMA_PEER_MAX_ROWS 64
+
+int blum_llama_set_peer_allreduce(blum_ctx* ctx, blum_llama* m, int enable, int timeout_ms) {
+    if (!ctx) return BLUM_ERR_INVALID;
+    BLUM_REQUIRE(ctx, m != nullptr, "llama_set_peer_allreduce: null model");
+    if ((enable != 0) == (m->peer != nullptr)) return BLUM_OK;
+    BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);      // captured steps name the buffers of the other path
+    m->graphs.clear();
+    if (!enable) {
+        blum_peer_destroy(ctx, m->peer);
+        m->peer = nullptr;
+        return BLUM_OK;
+    }
+    if (m->cfg.tp_size <= 1 || !m->comm) return blum_fail(ctx, BLUM_ERR_STATE, "llama_set_peer_allreduce: needs tp_size > 1 and a communicator");
+    return blum_peer_create(ctx, m->comm, (int64_t)act_bytes(m, m->cfg.hidden), LLAMA_PEER_MAX_ROWS, timeout_ms, &m->peer);
+}
+int blum_llama_peer_allreduce(const blum_llama* m) { return m && m->peer ? 1 : 0; }
 
 int blum_llama_generate_weights(blum_ctx* ctx, blum_llama* m, uint64_t seed) {
     if (!ctx) return BLUM_ERR_INVALID;

@@ -149,6 +149,16 @@ class Llama:
         self.ctx._check(self.ctx.lib.blum_llama_set_comm(self.ctx.h, self.h, comm.h))
         self.comm = comm
 
+    def set_peer_allreduce(self, enable=True, timeout_ms=30000):
+        """Tensor-parallel shards: sum row-parallel projections over peer-mapped memory in one kernel (steps of up to 64
+        rows) instead of NCCL all-reduce + add.  Collective: every rank calls it.  Raises BlumError when the exchange
+        areas cannot be mapped (then nothing changed and NCCL stays in use)."""
+        self.ctx._check(self.ctx.lib.blum_llama_set_peer_allreduce(self.ctx.h, self.h, int(bool(enable)), int(timeout_ms)))
+
+    @property
+    def peer_allreduce(self):
+        return bool(self.ctx.lib.blum_llama_peer_allreduce(self.h))
+
     def generate_weights(self, seed):
         self.ctx._check(self.ctx.lib.blum_llama_generate_weights(self.ctx.h, self.h, seed))
 

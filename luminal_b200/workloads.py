@@ -6,7 +6,7 @@ import time
 
 import numpy as np
 
-from . import BF16, F32, Context
+from . import BF16, F32, BlumError, Context
 from .llama import LLAMA3_8B, LLAMA3_70B, Llama
 from .runtime import gen_token_ids, gen_normal, round_to_dtype
 
@@ -89,36 +89,69 @@ def tp70b(ctx: Context, comm, rank, world, steps, warmup, batch=16, prompt=1024,
         toks.append(model.prefill(s, gen_token_ids(seed, 10 + b, prompt, cfg["vocab"])))
     ctx.sync()
     prefill_s = time.perf_counter() - t0
-    for _ in range(max(warmup, 3)):
-        toks = model.decode(seqs, toks)
-    ctx.sync()
-    ctx.timer_start(5)
-    for _ in range(steps):
-        toks = model.decode(seqs, toks)
-    ctx.timer_stop(5)
-    ms = ctx.timer_ms(5)
-    ctx.check_device_error()
-    # the exchanges of one step alone: 2 all-reduces per layer of [batch, hidden] bf16, back to back on the same stream
-    ar_ms = 0.0
+    def timed_steps(toks):
+        for _ in range(max(warmup, 3)):
+            toks = model.decode(seqs, toks)
+        ctx.sync()
+        ctx.timer_start(5)
+        for _ in range(steps):
+            toks = model.decode(seqs, toks)
+        ctx.timer_stop(5)
+        return toks, ctx.timer_ms(5)
+
+    toks, ms = timed_steps(toks)
+    ms_nccl, exchange = None, "none (one GPU)"
     if world > 1:
-        buf = ctx.alloc(batch * cfg["hidden"] * 2)
-        for timed in (False, True):
-            if timed:
-                ctx.sync()
-                ctx.timer_start(6)
-            for _ in range(2 * cfg["layers"] * (4 if timed else 1)):
-                comm.allreduce_sum(buf, batch * cfg["hidden"], BF16)
-            if timed:
-                ctx.timer_stop(6)
-                ar_ms = ctx.timer_ms(6) / 4
+        # the same steps with the row-parallel sums done by one kernel over peer-mapped memory instead of NCCL + add
+        ms_nccl, exchange = ms, "NCCL all-reduce + add"
+        try:
+            model.set_peer_allreduce(True)
+            toks, ms = timed_steps(toks)
+            exchange = "one kernel over peer-mapped memory (sum over ranks + residual + RMSNorm)"
+        except BlumError as e:
+            exchange = "NCCL all-reduce + add (peer mapping failed: %s)" % e.message
+    ctx.check_device_error()
+    # the exchanges of one step alone, back to back on the same stream: 2 per layer of [batch, hidden] bf16, as NCCL
+    # all-reduce + add and as the one-kernel exchange over peer memory (which also normalises)
+    ar_ms, px_ms = 0.0, None
+    if world > 1:
+        n_ex, H = 2 * cfg["layers"], cfg["hidden"]
+        buf, res = ctx.alloc(batch * H * 2), ctx.alloc(batch * H * 2)
+        ctx._check(ctx.lib.blum_memset(ctx.h, buf.ptr, 0, batch * H * 2))
+        ctx._check(ctx.lib.blum_memset(ctx.h, res.ptr, 0, batch * H * 2))
+
+        def loop(fn, timer):
+            for timed in (False, True):
+                if timed:
+                    ctx.sync()
+                    ctx.timer_start(timer)
+                for i in range(n_ex * (4 if timed else 1)):
+                    fn(i)
+            ctx.timer_stop(timer)
+            return ctx.timer_ms(timer) / 4
+
+        def nccl_exchange(i):
+            comm.allreduce_sum(buf, batch * H, BF16)
+            ctx._check(ctx.lib.blum_add(ctx.h, res.ptr, buf.ptr, res.ptr, BF16, batch * H))
+        ar_ms = loop(nccl_exchange, 6)
+        if model.peer_allreduce:
+            peer = C.c_void_p()
+            ctx._check(ctx.lib.blum_peer_create(ctx.h, comm.h, H * 2, batch, 30000, C.byref(peer)))
+            px_ms = loop(lambda i: ctx._check(ctx.lib.blum_allreduce_fused(ctx.h, peer, i % 2, res.ptr, None, cfg["rms_eps"], buf.ptr, res.ptr,
+                                                                           BF16, batch, H)), 7)
+            ctx.check_device_error()
+            ctx._check(ctx.lib.blum_peer_destroy(ctx.h, peer))
         buf.free()
+        res.free()
     out = {"metric": "tp_decode_tokens_per_s", "value": batch * steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
            "ms_per_step": ms / steps, "dtype": "bf16", "data": "synthetic", "scaling": "strong",
            "config": {"workload": "llama3-70b-shape Q8_0 TP%d, batch %d, prompt %d (seed %d)" % (world, batch, prompt, seed),
-                      "layers": cfg["layers"], "allreduce": "NCCL sum, 2 per layer, %d B each" % (batch * cfg["hidden"] * 2)},
+                      "layers": cfg["layers"], "exchange": exchange, "exchanges": "2 per layer, %d B each" % (batch * cfg["hidden"] * 2)},
+           "ms_per_step_nccl": None if ms_nccl is None else ms_nccl / steps,
            "weight_bytes_per_gpu": model.weight_bytes,
            "achieved_weight_GBps_per_gpu": model.weight_bytes / (ms / steps) / 1e6,
-           "allreduce_ms_per_step": ar_ms, "allreduce_share": ar_ms / (ms / steps),
+           "nccl_exchange_ms_per_step": ar_ms, "nccl_exchange_share": ar_ms / ((ms_nccl or ms) / steps),
+           "peer_exchange_ms_per_step": px_ms, "peer_exchange_share": None if px_ms is None else px_ms / (ms / steps),
            "prefill": {"tokens": batch * prompt, "s": prefill_s, "tokens_per_s": batch * prompt / prefill_s}}
     model.destroy()
     return out
@@ -243,8 +276,18 @@ def tp_parity(ctx: Context, comm, rank, world, golden_npz):
     if world > 1:
         model.set_comm(comm)
     model.generate_weights(0)
-    got = model.greedy(gen_token_ids(0, 1, 6, cfg["vocab"]), 8)
+    prompt = gen_token_ids(0, 1, 6, cfg["vocab"])
+    got = [int(t) for t in model.greedy(prompt, 8)]
+    want = np.load(golden_npz)["tp_greedy_ids_f32"].tolist()
+    out = {"ids": got, "golden": want, "identical": got == want, "tp": world}
+    if world > 1:
+        try:
+            model.set_peer_allreduce(True)
+            peer = [int(t) for t in model.greedy(prompt, 8)]
+            out["ids_peer_exchange"] = peer
+            out["identical"] = out["identical"] and peer == want
+        except BlumError as e:
+            out["ids_peer_exchange"] = "peer mapping failed: %s" % e.message
     ctx.check_device_error()
     model.destroy()
-    want = np.load(golden_npz)["tp_greedy_ids_f32"].tolist()
-    return {"ids": [int(t) for t in got], "golden": want, "identical": [int(t) for t in got] == want, "tp": world}
+    return out

@@ -102,3 +102,34 @@ def test_stream_decode_loop_and_repack_after_weight_change(ctx, orc):
     assert m.greedy(prompt, 8) == ids
     ctx.check_device_error()
     m.destroy()
+
+
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_B], ids=["hidden512", "hidden1024"])
+def test_prompt_chunks_take_the_packed_rows_matmul(ctx, orc, cfg):
+    """Prompt chunks of the f32 configuration multiply 8 / 16 / 32 rows per pass over the stream-packed weights
+    (integer mma on block-fixed-point rows): logits of the last prompt token against the oracle for every tile shape,
+    a ragged last tile and more rows than one scratch block; the per-op path (GEMV, two rows per pass) agrees too."""
+    m, w = _pair(ctx, orc, cfg, seed=8, max_ctx=160)
+    for n in (5, 9, 17, 33, 131):
+        prompt = orc.gen_token_ids(8, n, n, cfg["vocab"])
+        ref = orc.Llama(cfg, w, ctx_cap=160)
+        want = ref.forward(prompt)
+        seq = m.new_sequence()
+        tok, logits = m.prefill(seq, prompt, want_logits=True)
+        m.kv.seq_free(seq)
+        assert_parity(logits, want, max_abs=1e-3, rel=1e-3, what="prompt of %d tokens" % n)
+        assert tok == orc.argmax(want)
+        ctx._check(ctx.lib.blum_llama_set_decode_path(ctx.h, m.h, 1))
+        seq = m.new_sequence()
+        tok1, logits1 = m.prefill(seq, prompt, want_logits=True)
+        m.kv.seq_free(seq)
+        ctx._check(ctx.lib.blum_llama_set_decode_path(ctx.h, m.h, 0))
+        assert tok1 == tok
+        assert_parity(logits1, logits, max_abs=1e-4, rel=1e-4, what="per-op path, prompt of %d tokens" % n)
+        # a second pass gives the same bits (fixed summation order)
+        seq = m.new_sequence()
+        _, logits2 = m.prefill(seq, prompt, want_logits=True)
+        m.kv.seq_free(seq)
+        assert np.array_equal(logits, logits2)
+    ctx.check_device_error()
+    m.destroy()
