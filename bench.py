@@ -26,7 +26,7 @@ CFG = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=143
 PROMPT_LEN = 32
 SEED = 0
 # DRAM bytes / algorithmic bytes of decode_stream_kernel, from the ncu capture summarised in profiles/decode_stream_8b_4layers.md
-NCU_TRAFFIC_RATIO = None
+NCU_TRAFFIC_RATIO = 1.0075   # DRAM bytes / algorithmic bytes of decode_stream_kernel (profiles/decode_stream_8b_4layers.md)
 
 
 def measured_peaks():
@@ -402,7 +402,9 @@ def run_secondary(args, rank, world, local_rank):
         if rank == 0:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
             ms = [int(v) for v in args.m.split(",")] if args.m else None
-            print(json.dumps(workloads.sweep(ctx, ms=ms, iters=max(args.steps, 5), hbm_peak=float(peaks.get("hbm_gbs", 6650.0)),
+            shapes = [tuple(int(v) for v in sh.split("x")) for sh in args.shapes.split(",")] if args.shapes else None
+            dt = {"bf16": 2, "f16": 1, "f32": 0}[args.dtype]
+            print(json.dumps(workloads.sweep(ctx, ms=ms, shapes=shapes, dtype=dt, iters=max(args.steps, 5), hbm_peak=float(peaks.get("hbm_gbs", 6650.0)),
                                              tc_peak=float(peaks.get("bf16_tflops", 1590.0)))), flush=True)
     elif args.workload == "moe":
         if rank == 0:
@@ -443,6 +445,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="truncate the model to this many layers (small cases for profiler captures; the line says so)")
     ap.add_argument("--prompt", type=int, default=None, help="tp70b only: prompt length (default 1024)")
     ap.add_argument("--m", default=None, help="sweep only: comma-separated row counts (default 1,8,64,512,4096)")
+    ap.add_argument("--shapes", default=None, help="sweep only: comma-separated KxN (default: the four shapes of the operator sweep)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16", "f32"], help="sweep only: activation / output type")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -166,6 +166,16 @@ int blum_softmax(blum_ctx* ctx, const void* x, void* y, blum_dtype dtype, int64_
  * row; among equal maxima the LAST index wins (Iterator::max_by semantics); NaNs compare equal. */
 int blum_argmax(blum_ctx* ctx, const void* logits, blum_dtype dtype, int64_t rows, int64_t cols,
                 int32_t* out_idx);
+/* Temperature / top-p sampler, one token per row of f32 logits (no counterpart in the reference, which only has the
+ * greedy rule above).  Integer-exact specification, so every implementation gives the same token: m = largest non-NaN
+ * logit; z = (l - m) * (1 / temperature) in f32; w = trunc(2^30 e^z) by a fixed sequence of f32 operations; W = sum w;
+ * P = max(1, (uint64)((double)top_p * W)) (W for top_p >= 1); tau = largest integer with S(tau) = sum of the w >= tau
+ * reaching P; r = floor(u * S(tau) / 2^64) with u = mix64(mix64(seed + GOLDEN * (seq + 1)) + pos); the token is the first
+ * index with w >= tau, in index order, whose running sum of w exceeds r.  row_seq / row_pos: device int32 [rows] (NULL:
+ * zeros).  scratch: device memory of rows * cols * 4 bytes.  A row without a finite logit, or whose maximum is +inf, is
+ * sampled greedily. */
+int blum_sample_top_p(blum_ctx* ctx, const float* logits, int64_t rows, int64_t cols, float temperature, float top_p,
+                      uint64_t seed, const int32_t* row_seq, const int32_t* row_pos, void* scratch, int32_t* out_idx);
 
 /* ------------------------------------------------------------------ paged KV cache
  * The reference cache is one contiguous [1, kv_heads, pos, head_dim] tensor per layer that is
@@ -346,6 +356,10 @@ int blum_llama_set_tensor(blum_ctx* ctx, blum_llama* m, const char* gguf_name, c
                           size_t nbytes, int is_q8_0);
 uint64_t blum_llama_tensor_id(const char* gguf_name);
 int blum_llama_set_comm(blum_ctx* ctx, blum_llama* m, blum_comm* comm);
+/* Next-token rule of prefill / decode / decode_loop.  temperature = 0 (the default) is the reference's greedy rule
+ * (examples/llama/src/main.rs:194-198); temperature > 0 samples with blum_sample_top_p keyed by (seed, sequence slot,
+ * position), so the same seed reproduces the same text.  No counterpart in the reference for temperature > 0. */
+int blum_llama_set_sampling(blum_ctx* ctx, blum_llama* m, float temperature, float top_p, uint64_t seed);
 /* Tensor-parallel models only (no counterpart in the reference): enable = 1 makes steps of up to 64 rows sum their
  * row-parallel projections with blum_allreduce_fused over a peer-mapped area (collective: every rank must call it);
  * enable = 0 returns to NCCL all-reduce + add.  Larger row counts always use NCCL. */

@@ -78,6 +78,9 @@ struct blum_llama {
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;   // (rows, nsplit) -> captured decode step
     std::map<std::pair<int, int>, int> graph_nodes;          // kernel nodes per captured step
     blum_comm* comm = nullptr;
+    float temperature = 0.f, top_p = 1.f;   // temperature 0: greedy (the reference's sampler)
+    uint64_t sample_seed = 0;
+    void* sample_scratch = nullptr;    // integer weights of the sampled rows [max_seqs][vocab]
     void* rows_scratch = nullptr;      // digitised activations and partial sums of the prompt-chunk matmul (prefill_rows.cu)
     size_t rows_scratch_bytes = 0;
     blum_peer* peer = nullptr;         // peer-mapped exchange area: row-parallel sums without a library collective
@@ -108,6 +111,14 @@ __global__ void advance_rows_kernel(int32_t* rows, int max_rows, const int32_t* 
 static size_t act_bytes(const blum_llama* m, int64_t elems) { return (size_t)elems * blum_dtype_size(m->cfg.act_dtype); }
 
 #define TRY(call) do { int rc__ = (call); if (rc__) return rc__; } while (0)
+
+// next-token choice for `rows` rows of logits: the reference's greedy rule, or the temperature / top-p sampler keyed by
+// (seed, sequence slot, position) of each row
+static int pick_tokens(blum_ctx* ctx, blum_llama* m, int rows, const int32_t* seq, const int32_t* pos) {
+    if (m->temperature > 0.f)
+        return blum_sample_top_p(ctx, m->logits, rows, m->vocab, m->temperature, m->top_p, m->sample_seed, seq, pos, m->sample_scratch, m->d_next);
+    return blum_argmax(ctx, m->logits, BLUM_F32, rows, m->vocab, m->d_next);
+}
 
 static bool stream_supported(blum_ctx* ctx, blum_llama* m);
 static int build_stream_plan(blum_ctx* ctx, blum_llama* m);
@@ -259,7 +270,7 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         TRY(blum_pick_pairs(ctx, m->d_pairs, c.tp_size, HR, m->d_next));
         return BLUM_OK;
     }
-    TRY(blum_argmax(ctx, m->logits, BLUM_F32, HR, m->vocab, m->d_next));
+    TRY(pick_tokens(ctx, m, HR, seq + (last_row_only ? R - 1 : 0), pos + (last_row_only ? R - 1 : 0)));
     return BLUM_OK;
 }
 
@@ -387,7 +398,7 @@ static int run_stream_launch(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) 
 }
 static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
     TRY(run_stream_launch(ctx, m, max_ctx_len));
-    return blum_argmax(ctx, m->logits, BLUM_F32, 1, m->vocab, m->d_next);
+    return pick_tokens(ctx, m, 1, m->d_rows + m->max_rows, m->d_rows + 2 * m->max_rows);
 }
 
 static int run_decode_step(blum_ctx* ctx, blum_llama* m, int R, int nsplit, int64_t max_ctx_len) {
@@ -484,7 +495,7 @@ int blum_llama_destroy(blum_ctx* ctx, blum_llama* m) {
     }
     if (!m->cfg.tie_head) blum_q8_0_weight_free(ctx, m->head);
     blum_q8_0_weight_free(ctx, m->embed_q8);
-    void* bufs[] = {m->rows_scratch, m->embed_f32, m->out_norm, m->x, m->xn, m->qkv, m->q, m->attn, m->mid, m->gate, m->up, m->logits,
+    void* bufs[] = {m->sample_scratch, m->rows_scratch, m->embed_f32, m->out_norm, m->x, m->xn, m->qkv, m->q, m->attn, m->mid, m->gate, m->up, m->logits,
                     m->d_rows, m->d_next, m->d_hist, m->attn_scratch, m->d_pairs};
     for (void* b : bufs) if (b) cudaFree(b);
     if (m->h_rows) cudaFreeHost(m->h_rows);
@@ -677,6 +688,21 @@ int blum_llama_set_peer_allreduce(blum_ctx* ctx, blum_llama* m, int enable, int 
     return blum_peer_create(ctx, m->comm, (int64_t)act_bytes(m, m->cfg.hidden), LLAMA_PEER_MAX_ROWS, timeout_ms, &m->peer);
 }
 int blum_llama_peer_allreduce(const blum_llama* m) { return m && m->peer ? 1 : 0; }
+
+int blum_llama_set_sampling(blum_ctx* ctx, blum_llama* m, float temperature, float top_p, uint64_t seed) {
+    if (!ctx) return BLUM_ERR_INVALID;
+    BLUM_REQUIRE(ctx, m != nullptr, "llama_set_sampling: null model");
+    BLUM_REQUIRE(ctx, temperature >= 0.f && top_p > 0.f, "llama_set_sampling: temperature must be >= 0 and top_p > 0");
+    if (temperature > 0.f && m->cfg.tp_size > 1)
+        return blum_fail(ctx, BLUM_ERR_STATE, "llama_set_sampling: a vocabulary-parallel head only samples greedily");
+    BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (temperature > 0.f && !m->sample_scratch)
+        BLUM_CUDA(ctx, cudaMalloc(&m->sample_scratch, (size_t)std::max(m->cfg.max_seqs, 1) * (size_t)m->vocab * 4));
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);      // captured steps end in the other kernel
+    m->graphs.clear();
+    m->temperature = temperature; m->top_p = top_p; m->sample_seed = seed;
+    return BLUM_OK;
+}
 
 int blum_llama_generate_weights(blum_ctx* ctx, blum_llama* m, uint64_t seed) {
     if (!ctx) return BLUM_ERR_INVALID;

@@ -149,6 +149,11 @@ class Llama:
         self.ctx._check(self.ctx.lib.blum_llama_set_comm(self.ctx.h, self.h, comm.h))
         self.comm = comm
 
+    def set_sampling(self, temperature=0.0, top_p=1.0, seed=0):
+        """temperature 0: greedy (the reference's rule); otherwise temperature / top-p sampling keyed by (seed, sequence
+        slot, position): the same seed reproduces the same tokens."""
+        self.ctx._check(self.ctx.lib.blum_llama_set_sampling(self.ctx.h, self.h, float(temperature), float(top_p), int(seed)))
+
     def set_peer_allreduce(self, enable=True, timeout_ms=30000):
         """Tensor-parallel shards: sum row-parallel projections over peer-mapped memory in one kernel (steps of up to 64
         rows) instead of NCCL all-reduce + add.  Collective: every rank calls it.  Raises BlumError when the exchange

@@ -257,6 +257,67 @@ int32_t orc_argmax(const float* v, int64_t n) {
     return (int32_t)best;
 }
 
+/* Temperature / top-p sampler.  The reference only samples greedily (examples/llama/src/main.rs:194-198); this sampler has
+ * no counterpart there and is specified here, in integers wherever a result could depend on the order of operations, so
+ * that a parallel implementation reproduces it bit for bit:
+ *   m    = the largest logit that is not a NaN (a row without one falls back to the greedy rule)
+ *   z_i  = (l_i - m) * (1 / temperature), each operation rounded to f32
+ *   w_i  = trunc(2^30 * e^z_i) by orc_sample_weight below (a fixed sequence of f32 operations); NaN and -inf give 0
+ *   W    = sum of w_i;  P = max(1, (uint64)((double)top_p * (double)W)), P = W for top_p >= 1
+ *   tau  = the largest integer with S(tau) = sum of the w_i >= tau  >=  P;  the nucleus is {i : w_i >= tau}
+ *   r    = floor(u * S(tau) / 2^64), u = mix64(mix64(seed + GOLDEN * (seq + 1)) + pos)
+ *   the sampled token is the first index i of the nucleus, in index order, whose running sum of w exceeds r. */
+static uint32_t orc_sample_weight(float z) {
+    if (!(z > -21.5f)) return 0;                      /* also NaN; 2^30 e^-21.5 < 1 */
+    if (z > 0.f) z = 0.f;
+    const float t = z * 1.44269504f;
+    const float n = rintf(t);                         /* round to nearest even */
+    const float f = t - n;                            /* exact, |f| <= 0.5 */
+    float p = 1.5403530e-4f;                          /* 2^f = e^(f ln 2), Taylor coefficients, Horner with fused multiply-adds */
+    p = fmaf(p, f, 1.3333558e-3f);
+    p = fmaf(p, f, 9.6181291e-3f);
+    p = fmaf(p, f, 5.5504109e-2f);
+    p = fmaf(p, f, 2.4022651e-1f);
+    p = fmaf(p, f, 6.9314718e-1f);
+    p = fmaf(p, f, 1.0f);
+    union { uint32_t u; float v; } sc;
+    sc.u = (uint32_t)(127 + 30 + (int)n) << 23;       /* 2^(n + 30), n in [-32, 0] */
+    return (uint32_t)(p * sc.v);                      /* exact scaling, then truncation */
+}
+
+int32_t orc_sample_top_p(const float* logits, int64_t n, float temperature, float top_p, uint64_t seed, uint64_t seq, uint64_t pos) {
+    float m = -INFINITY; int any = 0;
+    for (int64_t i = 0; i < n; i++) if (logits[i] == logits[i]) { if (!any || logits[i] > m) m = logits[i]; any = 1; }
+    if (!any || !(m > -INFINITY) || !(temperature > 0.f)) return orc_argmax(logits, n);
+    const float inv_t = 1.0f / temperature;
+    uint32_t* w = (uint32_t*)malloc((size_t)n * sizeof(uint32_t));
+    uint64_t W = 0;
+    for (int64_t i = 0; i < n; i++) {
+        const float d = logits[i] - m;
+        w[i] = orc_sample_weight(d * inv_t);
+        W += w[i];
+    }
+    uint64_t P = top_p >= 1.f ? W : (uint64_t)((double)top_p * (double)W);
+    if (P < 1) P = 1;
+    uint32_t lo = 1, hi = 0x7fffffffu;                /* S(lo) >= P always holds for lo = 1 */
+    while (lo < hi) {
+        const uint32_t mid = lo + (hi - lo + 1) / 2;
+        uint64_t S = 0;
+        for (int64_t i = 0; i < n; i++) if (w[i] >= mid) S += w[i];
+        if (S >= P) lo = mid; else hi = mid - 1;
+    }
+    const uint32_t tau = lo;
+    uint64_t S = 0;
+    for (int64_t i = 0; i < n; i++) if (w[i] >= tau) S += w[i];
+    const uint64_t u = mix64(mix64(seed + 0x9E3779B97F4A7C15ull * (seq + 1)) + pos);
+    const uint64_t r = (uint64_t)(((unsigned __int128)u * S) >> 64);
+    uint64_t run = 0; int32_t pick = -1;
+    for (int64_t i = 0; i < n && pick < 0; i++)
+        if (w[i] >= tau) { run += w[i]; if (run > r) pick = (int32_t)i; }
+    free(w);
+    return pick < 0 ? orc_argmax(logits, n) : pick;
+}
+
 /* ------------------------------------------------------------------ attention
  * q [T, nq, d]; K,V contiguous caches [nkv, ctx_cap, d] holding p+T valid positions (the new rows already
  * appended at p..p+T, examples/llama/src/model.rs:108-110).  Scores S = (q.k)/sqrt(d) for j in [0,p+T), plus

@@ -32,6 +32,8 @@ def lib():
         L.orc_f32_to_f16.restype = C.c_uint16
         L.orc_f32_to_f16.argtypes = [C.c_float]
         L.orc_argmax.restype = C.c_int32
+        L.orc_sample_top_p.restype = C.c_int32
+        L.orc_sample_top_p.argtypes = [C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_uint64, C.c_uint64, C.c_uint64]
         L.orc_llama_forward.restype = C.c_int
         L.orc_num_threads.restype = C.c_int
         _lib = L
@@ -195,6 +197,12 @@ def triu(size, diagonal):
 def argmax(v):
     v = np.ascontiguousarray(v, dtype=np.float32).reshape(-1)
     return int(lib().orc_argmax(_p(v), _i64(v.size)))
+
+
+def sample_top_p(v, temperature, top_p, seed, seq, pos):
+    """Temperature / top-p sample of one row of logits (orc_sample_top_p: an integer-exact specification)."""
+    v = np.ascontiguousarray(v, dtype=np.float32).reshape(-1)
+    return int(lib().orc_sample_top_p(v.ctypes.data, v.size, float(temperature), float(top_p), int(seed), int(seq), int(pos)))
 
 
 def attention(q, kc, vc, T, p, nq, nkv, d, ctx_cap):

@@ -20,6 +20,9 @@ for p in (ROOT, os.path.dirname(HERE)):
 from helpers import TINY_CFG, TP_CFG, make_weights  # noqa: E402
 
 Q8_CASES = [(64, 256, 1), (96, 512, 3), (40, 1024, 8)]   # (N, K, M); tensor id 100+i, activations id 200+i, seed 1
+# temperature / top-p sampler: logits = gen_normal(seed 5, tensor 700, 8 x 1000, sigma 3); (temperature, top_p, seed) cases;
+# row r is sampled as sequence slot r % 3 at position 10 r + case index
+SAMPLE_CASES = [(1.0, 1.0, 1), (0.7, 0.9, 2), (2.0, 0.5, 3), (1.0, 0.02, 4)]
 
 
 def compute(orc):
@@ -64,6 +67,9 @@ def compute(orc):
         ids, gaps = model.greedy(orc.gen_token_ids(0, 1, 6, TP_CFG["vocab"]), 8)
         out[key] = np.array(ids, np.int32)
         out[key.replace("ids", "gaps")] = np.array(gaps, np.float32)
+    logits = orc.gen_normal(5, 700, 8 * 1000, 3.0).reshape(8, 1000)
+    out["sample_ids"] = np.array([[orc.sample_top_p(logits[r], t, p, sd, r % 3, 10 * r + c) for r in range(8)]
+                                  for c, (t, p, sd) in enumerate(SAMPLE_CASES)], np.int32)
     return out
 
 

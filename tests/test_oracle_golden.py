@@ -190,6 +190,29 @@ def test_sibling_decoders_against_float64_model(orc, cfg):
         assert_parity(a, b, max_abs=1e-4, rel=1e-4, what="decode logits")
 
 
+def test_sampler_specification(orc):
+    """The temperature / top-p sampler of the oracle: frequencies follow softmax(l / T), the nucleus is the smallest set of
+    most likely tokens reaching top_p (ties included), degenerate rows fall back to the greedy rule."""
+    rng = np.random.default_rng(3)
+    l = (rng.standard_normal(300) * 2).astype(np.float32)
+    for temp in (1.0, 0.5):
+        p = np.exp((l.astype(np.float64) - l.max()) / temp)
+        p /= p.sum()
+        n = 20000
+        cnt = np.bincount([orc.sample_top_p(l, temp, 1.0, 9, 1, i) for i in range(n)], minlength=300)
+        top = np.argsort(-p)[:8]
+        assert np.abs(cnt[top] / n - p[top]).max() < 4 * np.sqrt(p[top].max() / n) + 1e-3
+    order = np.argsort(-p)
+    k = int(np.searchsorted(np.cumsum(p[order]), 0.6)) + 1
+    seen = {orc.sample_top_p(l, 0.5, 0.6, 9, 0, i) for i in range(4000)}
+    assert seen <= set(order[:k + 1].tolist()) and len(seen) >= k - 1
+    assert {orc.sample_top_p(l, 1.0, 1e-9, 9, 0, i) for i in range(50)} == {int(np.argmax(l))}
+    assert orc.sample_top_p(np.full(10, np.nan, np.float32), 1.0, 1.0, 1, 0, 0) == orc.argmax(np.full(10, np.nan, np.float32))
+    inf = l.copy(); inf[7] = np.inf
+    assert orc.sample_top_p(inf, 1.0, 1.0, 1, 0, 0) == 7
+    assert orc.sample_top_p(l, 1.0, 0.9, 5, 2, 40) == orc.sample_top_p(l, 1.0, 0.9, 5, 2, 40)       # a pure function of its key
+
+
 def test_golden_fixture_matches_oracle(orc):
     """tests/golden/oracle_vectors.npz (written by tests/golden/make_golden.py) is reproduced: integer results
     exactly, float results to 1e-6 relative (libm may differ in the last place between CPUs)."""
