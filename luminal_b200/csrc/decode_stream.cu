@@ -36,7 +36,6 @@
 
 #define DS_TIMEOUT_NS 2000000000ull       // every wait gives up after 2 s
 #define LOG2E 1.4426950408889634f
-#define DS_STAGE_UNROLL 4
 
 __device__ __forceinline__ uint32_t ds_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ds_mbar_init(uint64_t* bar, uint32_t count) {
@@ -132,7 +131,8 @@ struct DsShared {
     float partial[DS_PARTIAL_SLOTS][16];            // per-unit row sums waiting for the rest of their group
     int gcnt[DS_PARTIAL_SLOTS];                     // units of a group deposited so far (indexed by group % slots)
     int pbusy[DS_PARTIAL_SLOTS];                    // 1 while a slot of `partial` holds sums that have not been added up yet
-    float wred[DS_WARPS];                           // sum of squares per warp
+    int xstate[DS_MAX_SLICES];                      // 4 * phase + {1: being staged, 2: staged} per 512-element slice of x
+    float xss[DS_MAX_SLICES];                       // sum of squares of each staged slice (RMSNorm)
     float q[128], knew[128], vnew[128];
     float rsn[64], rcs[64];                         // rotation of the step's position
     float sc[DS_ATTN_TILE];
@@ -143,7 +143,9 @@ struct DsShared {
     int abort;
     float resid[DS_RESIDUAL_ROWS];                  // residual rows of the groups this CTA finishes (o_proj / down)
     float pp_sum[16];                               // partial sums of the later CTAs for this CTA's last group
-    int pp_state;                                   // 1: pp_sum is valid
+    int pp_state;                                   // phase + 1: pp_sum is valid for that phase
+    unsigned long long amax;                        // largest (ordered logit, row) key of this CTA's head rows; 0: none
+    int amax_nan;                                   // a head row of this CTA was a NaN
     int2 range[DS_MAX_PHASES];                      // this CTA's units [x, y) of every phase
 };
 
@@ -153,27 +155,24 @@ __device__ __forceinline__ uint32_t ds_tag(unsigned long long seq, int nphases, 
 }
 
 // ---- x of a phase -> block fixed point in shared memory (three signed byte planes + one scale per 32 elements)
-// planes: [K/32][3][32] bytes; scales: [K/32] floats.  Returns rsqrt(mean(x^2) + eps) when a norm weight is folded in.
-// x is the previous phase's output: tagged words that are loaded again until they carry that phase's tag.
-__device__ __forceinline__ float ds_stage_x(const DsParams& p, const DsPhase& P, int ph, unsigned long long seq, DsShared& sh,
-                                            unsigned char* xpl, float* xsc, int tid_c, volatile int* s_abort) {
-    const int K = P.K, lane = tid_c & 31, cw = tid_c >> 5;
+// planes: [K/32][3][32] bytes; scales: [K/32] floats.  x is the previous phase's output: tagged words that are loaded
+// again until they carry that phase's tag.  x is staged lazily, one 512-element slice (the k range of one unit) at a time,
+// by the warp that first needs it: a unit only needs its own slice, so a warp starts on its weights as soon as that slice
+// has arrived instead of waiting for the slowest producer of the whole vector, and the round trips of the hand-over
+// overlap with the other warps' work.  sh.xstate[s] = 4 * phase + {1: a warp is staging it, 2: staged}.
+__device__ __noinline__ void ds_stage_slice(const DsParams& p, int kind, int layer, const float* norm_w, int ph, unsigned long long seq,
+                                            DsShared& sh, unsigned char* xpl, float* xsc, int lane, int slice, volatile int* s_abort) {
     const uint32_t tag = ds_tag(seq, p.nphases, ph - 1);
-    const unsigned long long* src = P.kind == DS_O ? p.attn : P.kind == DS_DOWN ? p.mid : p.xres;
-    const bool from_embed = (P.kind == DS_QKV && P.layer == 0);
-    const bool combine = (P.kind == DS_O) && p.nsplit > 1;
-    const float* erow = nullptr;
-    if (from_embed) {
-        int id = p.rows[0];
-        if (id < 0 || id >= p.vocab) { if (tid_c == 0) atomicOr(p.err, 0x100); id = 0; }
-        erow = p.embed + (size_t)id * p.H;
-    }
+    const unsigned long long* src = kind == DS_O ? p.attn : kind == DS_DOWN ? p.mid : p.xres;
+    const bool from_embed = (kind == DS_QKV && layer == 0);
+    const bool combine = (kind == DS_O) && p.nsplit > 1;
+    const int kbase = slice * DS_UNIT_K;
     float ss = 0.f;
     // one step of four consecutive elements: norm weight, block maximum over the 8 lanes of a 32-element block, digits
     auto put = [&](float (&v)[4], int k) {
         ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-        if (P.norm_w) {
-            const float4 nw = __ldg(reinterpret_cast<const float4*>(P.norm_w + k));
+        if (norm_w) {
+            const float4 nw = __ldg(reinterpret_cast<const float4*>(norm_w + k));
             v[0] *= nw.x; v[1] *= nw.y; v[2] *= nw.z; v[3] *= nw.w;
         }
         float mx = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
@@ -202,45 +201,49 @@ __device__ __forceinline__ float ds_stage_x(const DsParams& p, const DsPhase& P,
         *reinterpret_cast<unsigned*>(blk + 64) = pc;
         if ((k & 31) == 0) xsc[k >> 5] = down;
     };
-    constexpr int STEP = DS_THREADS * 4;
+    constexpr int PASS = 128;                                     // elements a warp covers per pass (4 per lane)
     if (from_embed) {
         // layer 0 reads the embedding row itself
-        for (int k = tid_c * 4; k < K; k += STEP) {
+        int id = p.rows[0];
+        if (id < 0 || id >= p.vocab) { if (lane == 0) atomicOr(p.err, 0x100); id = 0; }
+        const float* erow = p.embed + (size_t)id * p.H;
+#pragma unroll
+        for (int i = 0; i < DS_UNIT_K / PASS; i++) {
+            const int k = kbase + i * PASS + lane * 4;
             const float4 e = __ldg(reinterpret_cast<const float4*>(erow + k));
             float v[4] = {e.x, e.y, e.z, e.w};
             put(v, k);
         }
     } else if (!combine) {
-        for (int kb = 0; kb < K; kb += STEP * DS_STAGE_UNROLL) {               // (every thread runs every batch: the batch votes)
-            const int k0 = kb + tid_c * 4;
-            ulonglong2 buf[DS_STAGE_UNROLL][2];
-            // All words of the batch are requested together, and those that still carry an older tag are requested together
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int k0 = kbase + half * 2 * PASS + lane * 4;
+            ulonglong2 buf[2][2];
+            // All words of the round are requested together, and those that still carry an older tag are requested together
             // again: one round trip per attempt, however many of them are late.
             unsigned ready = 0;
             const unsigned long long t0 = blum_globaltimer();
             for (uint32_t spin = 0;; spin++) {
 #pragma unroll
-                for (int i = 0; i < DS_STAGE_UNROLL; i++)
-                    if (k0 + i * STEP < K && !((ready >> i) & 1u)) { buf[i][0] = ds_ld_word2(src + k0 + i * STEP); buf[i][1] = ds_ld_word2(src + k0 + i * STEP + 2); }
+                for (int i = 0; i < 2; i++)
+                    if (!((ready >> i) & 1u)) { buf[i][0] = ds_ld_word2(src + k0 + i * PASS); buf[i][1] = ds_ld_word2(src + k0 + i * PASS + 2); }
 #pragma unroll
-                for (int i = 0; i < DS_STAGE_UNROLL; i++)
-                    if (k0 + i * STEP >= K || (ds_tag_of(buf[i][0].x) == tag && ds_tag_of(buf[i][0].y) == tag && ds_tag_of(buf[i][1].x) == tag && ds_tag_of(buf[i][1].y) == tag))
+                for (int i = 0; i < 2; i++)
+                    if (ds_tag_of(buf[i][0].x) == tag && ds_tag_of(buf[i][0].y) == tag && ds_tag_of(buf[i][1].x) == tag && ds_tag_of(buf[i][1].y) == tag)
                         ready |= 1u << i;
-                if (ds_sync_and(ready == (1u << DS_STAGE_UNROLL) - 1u || *s_abort)) break;      // the same answer in every thread
-                if (tid_c == 0 && (spin & 15u) == 15u && !ds_aborted(p, s_abort) && blum_globaltimer() - t0 > DS_TIMEOUT_NS)
+                if (__all_sync(0xffffffffu, ready == 3u || *s_abort)) break;
+                if (lane == 0 && (spin & 15u) == 15u && !ds_aborted(p, s_abort) && blum_globaltimer() - t0 > DS_TIMEOUT_NS)
                     ds_give_up(p.err, p.ctr, s_abort, 2, (long long)tag, (long long)k0);
             }
 #pragma unroll
-            for (int i = 0; i < DS_STAGE_UNROLL; i++) {
-                const int k = k0 + i * STEP;
-                if (k < K) {
-                    float v[4] = {ds_val_of(buf[i][0].x), ds_val_of(buf[i][0].y), ds_val_of(buf[i][1].x), ds_val_of(buf[i][1].y)};
-                    put(v, k);
-                }
+            for (int i = 0; i < 2; i++) {
+                float v[4] = {ds_val_of(buf[i][0].x), ds_val_of(buf[i][0].y), ds_val_of(buf[i][1].x), ds_val_of(buf[i][1].y)};
+                put(v, k0 + i * PASS);
             }
         }
     } else {
-        for (int k = tid_c * 4; k < K; k += STEP) {
+        for (int i = 0; i < DS_UNIT_K / PASS; i++) {
+            const int k = kbase + i * PASS + lane * 4;
             // merge the split attention partials of head k/128: weights exp2((m_s - m_max) log2 e)
             const int h = k >> 7, c = k & 127;
             const unsigned long long* base = p.attn_part + (size_t)h * p.nsplit * 130;
@@ -257,23 +260,42 @@ __device__ __forceinline__ float ds_stage_x(const DsParams& p, const DsPhase& P,
             }
             const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll
-            for (int i = 0; i < 4; i++) v[i] *= inv;
+            for (int e = 0; e < 4; e++) v[e] *= inv;
             put(v, k);
         }
     }
-    if (P.norm_w) {
-        ss = warp_sum(ss);
-        if (lane == 0) sh.wred[cw] = ss;
+    ss = warp_sum(ss);
+    if (lane == 0) sh.xss[slice] = ss;
+}
+
+// makes sure slice `slice` of the phase's x is in shared memory: stages it, or waits for the warp that does
+__device__ __forceinline__ void ds_ensure_slice(const DsParams& p, const DsPhase& P, int ph, unsigned long long seq, DsShared& sh,
+                                                unsigned char* xpl, float* xsc, int lane, int slice, volatile int* s_abort) {
+    const int ready = ph * 4 + 2, busy = ph * 4 + 1;
+    int r = 0;
+    if (lane == 0) {
+        const int v = *reinterpret_cast<volatile int*>(&sh.xstate[slice]);
+        if (v == ready) r = 0;
+        else if (v == busy) r = 2;
+        else r = (atomicCAS(&sh.xstate[slice], v, busy) == v) ? 1 : 2;
     }
-    ds_sync();
-    float rs = 1.f;
-    if (P.norm_w) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < DS_WARPS; w++) s += sh.wred[w];
-        rs = rsqrtf(s / (float)K + p.eps);
+    r = __shfl_sync(0xffffffffu, r, 0);
+    if (r == 1) {
+        ds_stage_slice(p, P.kind, P.layer, P.norm_w, ph, seq, sh, xpl, xsc, lane, slice, s_abort);
+        __syncwarp();
+        if (lane == 0) { __threadfence_block(); *reinterpret_cast<volatile int*>(&sh.xstate[slice]) = ready; }
+    } else if (r == 2) {
+        if (lane == 0) {
+            const unsigned long long t0 = blum_globaltimer();
+            for (uint32_t spin = 1; *reinterpret_cast<volatile int*>(&sh.xstate[slice]) != ready && !*s_abort; spin++)
+                if ((spin & 1023u) == 0u && (ds_aborted(p, s_abort) || blum_globaltimer() - t0 > DS_TIMEOUT_NS)) {
+                    if (!*s_abort) ds_give_up(p.err, p.ctr, s_abort, 7, slice, ph);
+                    break;
+                }
+        }
+        __syncwarp();
     }
-    return rs;
+    __threadfence_block();
 }
 
 // (sequence, context length) of the step, validated
@@ -496,6 +518,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = tid_c; i < DS_PARTIAL_SLOTS; i += DS_THREADS) { sh.gcnt[i] = 0; sh.pbusy[i] = 0; }
+    for (int i = tid_c; i < DS_MAX_SLICES; i += DS_THREADS) sh.xstate[i] = 0;
+    if (tid_c == 0) { sh.pp_state = 0; sh.amax = 0ull; sh.amax_nan = 0; }
     __syncthreads();
 
     // ---- the weight stream.  Unit number n of this CTA's stream (all phases, in order) lives in ring stage n % NS, and
@@ -547,24 +571,24 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
         const int S = P.S, units = P.groups * S;
         const int u0 = sh.range[ph].x, u1 = sh.range[ph].y;
         if (u1 <= u0) continue;                   // nothing of this matrix here: its x is not needed either
-        const long long s0 = clock64();
         const uint32_t tag = ds_tag(seq, p.nphases, ph);
         long long* tl = (p.prof && P.layer == p.prof_layer && tid_c == 0) ? p.prof + (size_t)ncta * 32 + (size_t)cta * 64 + P.kind * 8 : nullptr;
         if (tl) tl[0] = (long long)blum_globaltimer();
-        ds_sync();                          // the previous phase's warps are done with x and the reduction scratch
-        if (tl) tl[1] = (long long)blum_globaltimer();
         // groups whose first slice this CTA holds finish here: [gh0, gh1); for o_proj / down their residual rows (written
-        // by the previous residual add, or the embedding row) are fetched together with x
+        // by the previous residual add, or the embedding row) are fetched now; the weight phase before this one does not
+        // use the buffer, so warps that are still in it are not disturbed
         const int gh0 = (u0 + S - 1) / S, gh1 = (u1 + S - 1) / S;
         if (P.kind == DS_O || P.kind == DS_DOWN) {
             const uint32_t rtag = ds_tag(seq, p.nphases, P.kind == DS_O ? ph - 3 : ph - 2);
             const int nres = min((gh1 - gh0) * DS_UNIT_ROWS, DS_RESIDUAL_ROWS);
             for (int i = tid_c; i < nres; i += DS_THREADS) sh.resid[i] = ds_wait_value(p.xres + (size_t)gh0 * DS_UNIT_ROWS + i, rtag, p, s_abort, 2);
         }
+        ds_sync();                          // the previous phase's warps are done with x and the reduction scratch
+        if (tl) tl[1] = (long long)blum_globaltimer();
         // The ring is full and stays so while x is waited for and staged.  So that HBM does not idle meanwhile, every warp
         // pulls the next units of its stage into L2 (a bounded distance ahead: more of it fills the queues that the
         // activation words have to pass through); the requests that follow the stall then hit L2.
-        if (lane == 0) {
+        auto pull_ahead = [&]() {            // lane 0 only
             DsCursor pc = rf;
             int pn = rf_n;
             for (int d = 0; d < DS_PREFETCH_UNITS && pc.base; d++) {
@@ -572,17 +596,13 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
                 ds_cursor_advance(phases, p.nphases, sh, pc, NS);
                 pn += NS;
             }
-        }
-        if (tid_c == 0) sh.pp_state = 0;
+        };
+        if (lane == 0) pull_ahead();
         if (tl) tl[2] = (long long)blum_globaltimer();
-        const float rs = ds_stage_x(p, P, ph, seq, sh, xpl, xsc, tid_c, s_abort);
-        if (tl) tl[3] = (long long)blum_globaltimer();
         if (ph + 1 < p.nphases) {                 // the norm weight of the phase after this one: towards L2, out of the way
             const DsPhase N = phases[ph + 1 + (phases[ph + 1].kind == DS_ATTN ? 1 : 0)];
             if (N.norm_w) for (int k = tid_c * 32; k < N.K; k += DS_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(N.norm_w + k));
         }
-        c_stage += clock64() - s0;
-        k_stage[P.kind] += clock64() - s0;
         const long long l0 = clock64();
         // the last group of the range continues in later CTAs if the range ends inside it
         const bool split_tail = (u1 % S != 0) && ((u1 / S) * S >= u0);
@@ -595,13 +615,19 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
             // The partial sums the later CTAs publish for this CTA's last group are fetched while the stream is still
             // running (one warp looks once per unit until they are there), so that finishing the group does not start a
             // chain of round trips at the very end of the phase.
-            if (split_tail && cw == NS - 1 && !sh.pp_state) {
+            if (split_tail && cw == NS - 1 && *reinterpret_cast<volatile int*>(&sh.pp_state) != ph + 1) {
                 float sum;
                 if (ds_fetch_partners(p, units, (u1 / S + 1) * S, cta, ncta, tag, lane, false, s_abort, sum)) {
                     if (lane < 16) sh.pp_sum[lane] = sum;
                     __syncwarp();
-                    if (lane == 0) { __threadfence_block(); sh.pp_state = 1; }
+                    if (lane == 0) { __threadfence_block(); *reinterpret_cast<volatile int*>(&sh.pp_state) = ph + 1; }
                 }
+            }
+            {
+                const long long e0 = clock64();
+                ds_ensure_slice(p, P, ph, seq, sh, xpl, xsc, lane, s, s_abort);
+                if (cw == 0) { c_stage += clock64() - e0; k_stage[P.kind] += clock64() - e0; }
+                if (tl && u == u0 + first) tl[3] = (long long)blum_globaltimer();
             }
             const long long f0 = clock64();
             ds_mbar_wait(&sh.full[cw], par, p, s_abort, 1, n);
@@ -690,18 +716,49 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
                     if (!has_tail) {
                         // the group continues in later CTAs: their partial sums, summed in CTA order, are added as one term
                         float sum;
-                        if (*reinterpret_cast<volatile int*>(&sh.pp_state)) { __threadfence_block(); sum = lane < 16 ? sh.pp_sum[lane] : 0.f; }
+                        if (*reinterpret_cast<volatile int*>(&sh.pp_state) == ph + 1) { __threadfence_block(); sum = lane < 16 ? sh.pp_sum[lane] : 0.f; }
                         else ds_fetch_partners(p, units, (grp + 1) * S, cta, ncta, tag, lane, true, s_abort, sum);
                         v += sum;
                     }
                     const int row = grp * DS_UNIT_ROWS + lane;
+                    // RMSNorm scale: every slice's sum of squares, in slice order (a group that continues in later CTAs has
+                    // not needed all slices here yet)
+                    float rs = 1.f;
+                    if (P.norm_w) {
+                        if (!has_tail)
+                            for (int sl = 0; sl < S; sl++) ds_ensure_slice(p, P, ph, seq, sh, xpl, xsc, lane, sl, s_abort);
+                        float ssq = 0.f;
+                        for (int sl = 0; sl < S; sl++) ssq += sh.xss[sl];
+                        rs = rsqrtf(ssq / (float)P.K + p.eps);
+                    }
                     if (P.kind == DS_GATEUP) {
                         const float upv = __shfl_down_sync(0xffffffffu, v, 8) * rs;         // rows 0-7 of a group are gate rows, 8-15 the up rows
                         const float gate = v * rs;
                         if (lane < 8) ds_st_tagged(p.mid + grp * 8 + lane, upv * (gate * (1.f / (1.f + __expf(-gate)))), tag);
                     } else if (lane < 16) {
                         if (P.kind == DS_QKV) ds_st_tagged(p.qkv + row, v * rs, tag);
-                        else if (P.kind == DS_HEAD) p.logits[row] = v * rs;
+                        else if (P.kind == DS_HEAD) {
+                            const float lv = v * rs;
+                            p.logits[row] = lv;
+                            if (p.pick) {
+                                // greedy rule of the reference: the LAST index holding the maximum.  Keys order like the
+                                // values (both zeros alike) with the row in the low half, so the larger row wins a tie.
+                                const bool isnan = lv != lv;
+                                uint32_t b = __float_as_uint(lv == 0.f ? 0.f : lv);
+                                b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+                                unsigned long long key = isnan ? 0ull : ((unsigned long long)b << 32) | (uint32_t)row;
+#pragma unroll
+                                for (int o = 8; o > 0; o >>= 1) {
+                                    const unsigned long long other = __shfl_xor_sync(0x0000ffffu, key, o);
+                                    key = other > key ? other : key;
+                                }
+                                const unsigned anynan = __ballot_sync(0x0000ffffu, isnan);
+                                if (lane == 0) {
+                                    atomicMax(&sh.amax, key);
+                                    if (anynan) sh.amax_nan = 1;
+                                }
+                            }
+                        }
                         else {                                                              // o_proj / down: residual add in place
                             const int ri = row - gh0 * DS_UNIT_ROWS;
                             const uint32_t rtag = ds_tag(seq, p.nphases, P.kind == DS_O ? ph - 3 : ph - 2);
@@ -726,6 +783,47 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
         long long* o = p.prof + cta * 32;
         for (int k = 0; k < 6; k++) { o[8 + 3 * k] = k_stage[k]; o[9 + 3 * k] = k_loop[k]; o[10 + 3 * k] = 0; }
         o[0] = clock64() - ct0; o[1] = c_full; o[2] = 0; o[3] = c_stage; o[4] = c_attn; o[5] = c_seg; o[6] = 0; o[7] = 0;
+    }
+    if (p.pick) {
+        // ---- next token inside the kernel: every CTA publishes its best (key, row); CTA 0 takes the maximum, and only when
+        // a NaN was seen anywhere replays the reference's sequential fold over the finished logits
+        ds_sync();                                                   // this CTA's head rows are all accounted for
+        const uint32_t atag = ds_tag(seq, p.nphases, p.nphases);
+        if (tid_c == 0) {
+            const unsigned long long key = sh.amax;
+            __threadfence();                                         // this CTA's logits before its word
+            ds_st_tagged(p.amax + (size_t)cta * 2, __uint_as_float((uint32_t)(key >> 32)), atag);
+            ds_st_tagged(p.amax + (size_t)cta * 2 + 1, __int_as_float(sh.amax_nan ? -2 : (key ? (int)(uint32_t)key : -1)), atag);
+        }
+        if (cta == 0) {
+            ds_sync();
+            if (tid_c == 0) { sh.amax = 0ull; sh.amax_nan = 0; }
+            ds_sync();
+            for (int c = tid_c; c < ncta; c += DS_THREADS) {
+                const unsigned long long hi = ds_wait_word(p.amax + (size_t)c * 2, atag, p, s_abort, 8);
+                const unsigned long long lo = ds_wait_word(p.amax + (size_t)c * 2 + 1, atag, p, s_abort, 8);
+                const int r = (int)(uint32_t)lo;
+                if (r == -2) sh.amax_nan = 1;
+                else if (r >= 0) atomicMax(&sh.amax, ((hi & 0xffffffffull) << 32) | (uint32_t)r);
+            }
+            ds_sync();
+            if (tid_c == 0 && !*s_abort) {
+                int tok = (int)(uint32_t)sh.amax;
+                if (sh.amax_nan) {
+                    __threadfence();
+                    float cur = *reinterpret_cast<volatile float*>(p.logits); tok = 0;
+                    for (int j = 1; j < p.vocab; j++) { const float v = *reinterpret_cast<volatile float*>(p.logits + j); if (!(cur > v)) { cur = v; tok = j; } }
+                }
+                p.next[0] = tok;
+                if (p.pick == 2) {
+                    // every CTA has finished every phase (its word is here), so nobody reads the row any more
+                    p.rows[0] = tok;
+                    p.rows[2 * p.max_rows] += 1;
+                    p.rows[3 * p.max_rows] += 1;
+                    if (p.hist) p.hist[p.hist_step] = tok;
+                }
+            }
+        }
     }
     // the launch number makes the next launch's tags new; whoever reads it has started, and nobody can finish before everybody
     // who has work has started (they all feed the last phase)

@@ -19,6 +19,7 @@
 #define DS_ATTN_PARTS (DS_THREADS / 128)   // partitions of a tile's positions in the P V product
 #define DS_PARTIAL_SLOTS 128                        // per-unit row sums in flight (power of two; > ring stages + 2 * warps + slices per group)
 #define DS_RESIDUAL_ROWS 512                        // residual rows a CTA keeps in shared memory per phase
+#define DS_MAX_SLICES 64                            // K / 512 of the widest matrix
 #define DS_PREFETCH_UNITS 2                         // units per warp pulled into L2 at the start of a phase
 
 enum { DS_QKV = 0, DS_ATTN = 1, DS_O = 2, DS_GATEUP = 3, DS_DOWN = 4, DS_HEAD = 5 };
@@ -37,11 +38,11 @@ struct DsParams {
     int nphases;
     KvView kv;
     int max_seqs, max_rows;
-    const int32_t* rows;         // ids | seq | pos | ctx, each [max_rows]; row 0 is the token of this step
+    int32_t* rows;               // ids | seq | pos | ctx, each [max_rows]; row 0 is the token of this step
     const float* embed;          // f32 [vocab][H]
     // activations that cross CTAs: 64-bit words {f32 value, tag of the launch and phase that wrote it}
     unsigned long long *xres, *qkv, *attn, *mid;
-    unsigned long long* done;        // [grid]: hint words, the tag of the last phase a CTA has finished
+    unsigned long long* amax;        // [grid][2]: every CTA's (largest logit as an ordered key, its row) of the head phase
     unsigned long long* part;        // [grid][16]: partial sums of a 16-row group that is split between CTAs
     unsigned long long* attn_part;   // [nq][nsplit][130]: split attention partials (o[128], max, sum)
     float* logits;
@@ -53,6 +54,12 @@ struct DsParams {
     int* err;
     long long* prof;             // development aid: per-CTA cycle counters [grid][32] + one layer's timeline [grid][64], or null
     int prof_layer;
+    // next-token choice inside the kernel (the reference's greedy rule): 0 off, 1 next[0] = argmax(logits), 2 also feeds the
+    // token back into rows (token, position + 1, context + 1) and records it in hist[hist_step]
+    int pick;
+    int32_t* next;
+    int32_t* hist;
+    int hist_step;
 };
 
 size_t blum_ds_smem_bytes(int kmax);

@@ -41,7 +41,7 @@ struct StreamPlan {
     int nphases = 0, kmax = 0, grid = 0;
     unsigned long long* words = nullptr;   // tagged activation words: xres | qkv | attn | mid | part | attn_part
     size_t words_bytes = 0;
-    unsigned long long *xres = nullptr, *qkv = nullptr, *attn = nullptr, *mid = nullptr, *part = nullptr, *attn_part = nullptr, *done = nullptr;
+    unsigned long long *xres = nullptr, *qkv = nullptr, *attn = nullptr, *mid = nullptr, *part = nullptr, *attn_part = nullptr, *amax = nullptr;
     unsigned long long* ctr = nullptr;
     size_t ctr_bytes = 0;
     long long* prof = nullptr;             // development aid (blum_llama_stream_profile)
@@ -326,11 +326,11 @@ static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
         if (e == cudaSuccess) e = cudaMalloc((void**)&sp.d_phases, sizeof(DsPhase) * (size_t)(5 * L + 1));
         const size_t n_x = (size_t)H, n_qkv = (size_t)qkv_rows, n_attn = (size_t)qd, n_mid = (size_t)m->ffn, n_part = (size_t)sp.grid * 16,
                      n_ap = (size_t)m->nq * DS_MAX_SPLITS * 130;
-        sp.words_bytes = (n_x + n_qkv + n_attn + n_mid + n_part + n_ap + (size_t)sp.grid) * sizeof(unsigned long long);
+        sp.words_bytes = (n_x + n_qkv + n_attn + n_mid + n_part + n_ap + 2 * (size_t)sp.grid) * sizeof(unsigned long long);
         if (e == cudaSuccess) e = cudaMalloc((void**)&sp.words, sp.words_bytes);
         if (e == cudaSuccess) {
             sp.xres = sp.words; sp.qkv = sp.xres + n_x; sp.attn = sp.qkv + n_qkv; sp.mid = sp.attn + n_attn; sp.part = sp.mid + n_mid;
-            sp.attn_part = sp.part + n_part; sp.done = sp.attn_part + n_ap;
+            sp.attn_part = sp.part + n_part; sp.amax = sp.attn_part + n_ap;
         }
         sp.ctr_bytes = 8 * sizeof(unsigned long long);
         if (e == cudaSuccess) e = cudaMalloc((void**)&sp.ctr, sp.ctr_bytes);
@@ -374,7 +374,8 @@ static int build_stream_plan(blum_ctx* ctx, blum_llama* m) {
     return BLUM_OK;
 }
 
-static int run_stream_launch(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
+// pick: 0 logits only, 1 greedy token into d_next[0], 2 also fed back into the step's row (hist[hist_step] records it)
+static int run_stream_launch(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len, int pick = 0, int hist_step = 0) {
     StreamPlan& sp = m->sp;
     if (!sp.built || sp.weights_version != m->weights_version) TRY(build_stream_plan(ctx, m));
     sp.last_ctx_len = max_ctx_len;
@@ -384,7 +385,7 @@ static int run_stream_launch(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) 
     p.kv = kv_view(m->kv); p.max_seqs = m->kv->max_seqs; p.max_rows = m->max_rows;
     p.rows = m->d_rows; p.embed = m->embed_f32;
     p.xres = sp.xres; p.qkv = sp.qkv; p.attn = sp.attn; p.mid = sp.mid; p.logits = m->logits;
-    p.part = sp.part; p.attn_part = sp.attn_part; p.done = sp.done; p.ctr = sp.ctr;
+    p.part = sp.part; p.attn_part = sp.attn_part; p.amax = sp.amax; p.ctr = sp.ctr;
     p.H = c.hidden; p.nq = m->nq; p.nkv = m->nkv; p.ffn = m->ffn; p.vocab = m->vocab;
     // enough (head, split) items to occupy the grid once contexts are long; one split per 256 cached positions at most
     int nsplit = (int)std::min<int64_t>(DS_MAX_SPLITS, std::max<int64_t>(1, max_ctx_len / 256));
@@ -394,15 +395,21 @@ static int run_stream_launch(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) 
     p.err = ctx->dev_error;
     p.prof = sp.prof;
     p.prof_layer = 3;
+    p.pick = pick; p.next = m->d_next; p.hist = m->d_hist; p.hist_step = hist_step;
     return blum_ds_launch(ctx, p);
 }
-static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len) {
-    TRY(run_stream_launch(ctx, m, max_ctx_len));
-    return pick_tokens(ctx, m, 1, m->d_rows + m->max_rows, m->d_rows + 2 * m->max_rows);
+// feed_step >= 0: the caller wants the token fed back on the device (decode loop); *fed says whether this step did it
+static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len, int feed_step, bool* fed) {
+    if (m->temperature > 0.f) {            // the sampler is a kernel of its own
+        TRY(run_stream_launch(ctx, m, max_ctx_len));
+        return pick_tokens(ctx, m, 1, m->d_rows + m->max_rows, m->d_rows + 2 * m->max_rows);
+    }
+    if (feed_step >= 0 && fed) *fed = true;
+    return run_stream_launch(ctx, m, max_ctx_len, feed_step >= 0 ? 2 : 1, feed_step >= 0 ? feed_step : 0);
 }
 
-static int run_decode_step(blum_ctx* ctx, blum_llama* m, int R, int nsplit, int64_t max_ctx_len) {
-    if (R == 1 && m->decode_path != 1 && stream_supported(ctx, m)) return run_stream_step(ctx, m, max_ctx_len);
+static int run_decode_step(blum_ctx* ctx, blum_llama* m, int R, int nsplit, int64_t max_ctx_len, int feed_step = -1, bool* fed = nullptr) {
+    if (R == 1 && m->decode_path != 1 && stream_supported(ctx, m)) return run_stream_step(ctx, m, max_ctx_len, feed_step, fed);
     auto key = std::make_pair(R, nsplit);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
@@ -894,9 +901,12 @@ int blum_llama_decode_loop(blum_ctx* ctx, blum_llama* m, int seq, int32_t first_
         TRY(upload_rows(ctx, m, 1));
         const int nsplit = pick_nsplit(ctx, m, 1, len + steps);
         for (int s = 0; s < steps; s++) {
-            TRY(run_decode_step(ctx, m, 1, nsplit, len + steps));
-            advance_rows_kernel<<<1, 32, 0, ctx->stream>>>(m->d_rows, m->max_rows, m->d_next, m->d_hist, s, 1);
-            BLUM_LAUNCH_CHECK(ctx);
+            bool fed = false;
+            TRY(run_decode_step(ctx, m, 1, nsplit, len + steps, s, &fed));
+            if (!fed) {
+                advance_rows_kernel<<<1, 32, 0, ctx->stream>>>(m->d_rows, m->max_rows, m->d_next, m->d_hist, s, 1);
+                BLUM_LAUNCH_CHECK(ctx);
+            }
         }
         if (tokens_out) BLUM_CUDA(ctx, cudaMemcpyAsync(tokens_out, m->d_hist, (size_t)steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
         return finish_step(ctx, m, "llama_decode_loop");
