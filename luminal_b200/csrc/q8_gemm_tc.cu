@@ -115,16 +115,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 // Weight formats the dequantising stage understands.
 enum { WF_Q8_0 = 0, WF_MXFP4 = 1, WF_BF16 = 2 };
 
-template <int TN, int WF> struct GtCfg {
+// KH: 64-wide k halves per pipeline stage.  One stage is one hand-over (barrier wait, MMA issue, commit) whatever it holds, and
+// at small token tiles that fixed cost, not the tensor work, sets the pace: two halves per stage halve the hand-overs.
+template <int TN, int WF, int KH = 1> struct GtCfg {
     static constexpr int A_BYTES = GT_BN * GT_BK * 2;       // 16384, bf16 weights in UMMA layout
     static constexpr int X_BYTES = TN * GT_BK * 2;          // bf16 activations
     // raw weight staging per stage: int8 [128][64], packed e2m1 nibbles [128][32], or none (bf16 lands in A directly)
     static constexpr int Q_BYTES = WF == WF_Q8_0 ? GT_BN * GT_BK : WF == WF_MXFP4 ? GT_BN * GT_BK / 2 : 0;
-    static constexpr int STAGE_BYTES = A_BYTES + X_BYTES + Q_BYTES;
+    static constexpr int HALF_BYTES = A_BYTES + X_BYTES + Q_BYTES;
+    static constexpr int STAGE_BYTES = KH * HALF_BYTES;
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;   // + alignment slack
     static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
-    static constexpr int TX_BYTES = (WF == WF_BF16 ? A_BYTES : Q_BYTES) + X_BYTES;
+    static constexpr int TX_BYTES = KH * ((WF == WF_BF16 ? A_BYTES : Q_BYTES) + X_BYTES);
 };
 
 // e2m1 code (sign, 2-bit exponent, 1-bit mantissa) -> value; codes 0..7 are {0, .5, 1, 1.5, 2, 3, 4, 6}
@@ -134,10 +137,11 @@ __device__ __forceinline__ float e2m1_value(int code) {
     return (code & 8) ? -mag : mag;
 }
 
-template <int TN, typename TY, int WF>
+template <int TN, typename TY, int WF, int KH>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, const GemmTcParams p) {
-    using C = GtCfg<TN, WF>;
+    using C = GtCfg<TN, WF, KH>;
+    static_assert(KH == 1 || WF == WF_Q8_0, "two halves per stage are built for Q8_0 weights only");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t full[8], a_ready[8], empty[8], acc_full, drained;
@@ -163,9 +167,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         nk = min(p.ksteps_total, ks0 + p.ksteps_per_split) - ks0;
     }
     const int KB = p.K >> 5;
-    auto a_s = [&](int s) { return smem + (size_t)s * C::STAGE_BYTES; };
-    auto x_s = [&](int s) { return smem + (size_t)s * C::STAGE_BYTES + C::A_BYTES; };
-    auto q_s = [&](int s) { return smem + (size_t)s * C::STAGE_BYTES + C::A_BYTES + C::X_BYTES; };
+    auto a_s = [&](int s, int h = 0) { return smem + (size_t)s * C::STAGE_BYTES + (size_t)h * C::HALF_BYTES; };
+    auto x_s = [&](int s, int h = 0) { return smem + (size_t)s * C::STAGE_BYTES + (size_t)h * C::HALF_BYTES + C::A_BYTES; };
+    auto q_s = [&](int s, int h = 0) { return smem + (size_t)s * C::STAGE_BYTES + (size_t)h * C::HALF_BYTES + C::A_BYTES + C::X_BYTES; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&a_ready[s], GT_CONV_WARPS); mbar_init(&empty[s], 1); }
@@ -202,11 +206,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 const int s = it % C::STAGES;
                 if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) - 1) & 1, abortp)) break;
                 mbar_expect_tx(&full[s], C::TX_BYTES);
-                const int k = (ks0 + it) * GT_BK;
-                if (WF == WF_Q8_0) tma_load_2d(q_s(s), &wmap, k, wrow0 + n0, &full[s]);
-                else if (WF == WF_MXFP4) tma_load_2d(q_s(s), &wmap, k / 2, wrow0 + n0, &full[s]);     // two weights per byte
-                else tma_load_2d(a_s(s), &wmap, k, wrow0 + n0, &full[s]);                              // bf16, 128-byte swizzle
-                tma_load_2d(x_s(s), &xmap, k, m0, &full[s]);
+#pragma unroll
+                for (int h = 0; h < KH; h++) {
+                    const int k = ((ks0 + it) * KH + h) * GT_BK;
+                    if (WF == WF_Q8_0) tma_load_2d(q_s(s, h), &wmap, k, wrow0 + n0, &full[s]);
+                    else if (WF == WF_MXFP4) tma_load_2d(q_s(s, h), &wmap, k / 2, wrow0 + n0, &full[s]);     // two weights per byte
+                    else tma_load_2d(a_s(s, h), &wmap, k, wrow0 + n0, &full[s]);                              // bf16, 128-byte swizzle
+                    tma_load_2d(x_s(s, h), &xmap, k, m0, &full[s]);
+                }
                 tma_issued = it + 1;
             }
         }
@@ -220,11 +227,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 ok = mbar_wait(&a_ready[s], (it / C::STAGES) & 1, abortp);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = umma_desc_sw128(smem_u32(a_s(s)));
-                const uint64_t bdesc = umma_desc_sw128(smem_u32(x_s(s)));
 #pragma unroll
-                for (int kk = 0; kk < GT_BK / 16; kk++)   // 16 bf16 = 32 bytes = 2 descriptor units along K
-                    umma_bf16(tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                for (int h = 0; h < KH; h++) {
+                    const uint64_t adesc = umma_desc_sw128(smem_u32(a_s(s, h)));
+                    const uint64_t bdesc = umma_desc_sw128(smem_u32(x_s(s, h)));
+#pragma unroll
+                    for (int kk = 0; kk < GT_BK / 16; kk++)   // 16 bf16 = 32 bytes = 2 descriptor units along K
+                        umma_bf16(tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (it > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                }
                 umma_commit(&empty[s]);
             }
             if (ok) umma_commit(&acc_full);
@@ -236,9 +246,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // Block scales come straight from global memory (L2); they are requested two k-steps before use so that
         // their latency is not paid once per stage after the weights have already landed.
         constexpr int CPT = 512 / (GT_CONV_WARPS * 32);         // Q8_0: 16-byte chunks per thread per stage
-        auto q8_scale = [&](int it, int i) -> float {
+        auto q8_scale = [&](int it, int h, int i) -> float {
             const int c = t + GT_CONV_WARPS * 32 * i, r = c >> 2, kq = c & 3;
-            const int nrow = n0 + r, kb = (ks0 + it) * 2 + (kq >> 1);
+            const int nrow = n0 + r, kb = ((ks0 + it) * KH + h) * 2 + (kq >> 1);
             return (it < nk && nrow < p.N && kb < KB) ? __half2float(__ldg(reinterpret_cast<const __half*>(p.scales) + (size_t)(wrow0 + nrow) * KB + kb)) : 0.f;
         };
         constexpr int FP4_TPR = GT_CONV_WARPS * 32 / GT_BN;      // MXFP4: threads per weight row per stage (32 packed bytes)
@@ -247,11 +257,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const int nrow = n0 + t / FP4_TPR, kb = (ks0 + it) * 2 + (t % FP4_TPR) / (FP4_TPR / 2);
             return (it < nk && nrow < p.N && kb < KB) ? __ldg(reinterpret_cast<const uint8_t*>(p.scales) + (size_t)(wrow0 + nrow) * KB + kb) : 0u;
         };
-        float sc[CPT], sc1[CPT], sc2[CPT];
+        float sc[KH][CPT], sc1[KH][CPT], sc2[KH][CPT];
         uint32_t e8 = 0, e8_1 = 0, e8_2 = 0;
         if (WF == WF_Q8_0) {
 #pragma unroll
-            for (int i = 0; i < CPT; i++) { sc[i] = q8_scale(0, i); sc1[i] = q8_scale(1, i); }
+            for (int h = 0; h < KH; h++)
+#pragma unroll
+                for (int i = 0; i < CPT; i++) { sc[h][i] = q8_scale(0, h, i); sc1[h][i] = q8_scale(1, h, i); }
         } else if (WF == WF_MXFP4) {
             e8 = fp4_scale(0); e8_1 = fp4_scale(1);
         }
@@ -259,27 +271,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const int s = it % C::STAGES;
             if (WF == WF_Q8_0) {
 #pragma unroll
-                for (int i = 0; i < CPT; i++) sc2[i] = q8_scale(it + 2, i);
+                for (int h = 0; h < KH; h++)
+#pragma unroll
+                    for (int i = 0; i < CPT; i++) sc2[h][i] = q8_scale(it + 2, h, i);
                 ok = mbar_wait(&full[s], (it / C::STAGES) & 1, abortp);
                 if (!ok) break;
-                const unsigned char* qs = q_s(s);
-                unsigned char* as = a_s(s);
 #pragma unroll
-                for (int i = 0; i < CPT; i++) {
-                    const int c = t + GT_CONV_WARPS * 32 * i, r = c >> 2, kq = c & 3;
-                    const int4 v = *reinterpret_cast<const int4*>(qs + c * 16);
-                    const int w[4] = {v.x, v.y, v.z, v.w};
-                    uint32_t o[8];
-                    const Q8Scale qs2 = q8_scale_consts(sc[i]);
+                for (int h = 0; h < KH; h++) {
+                    const unsigned char* qs = q_s(s, h);
+                    unsigned char* as = a_s(s, h);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) q8_dequant4((uint32_t)w[j], qs2, o[2 * j], o[2 * j + 1]);
-                    unsigned char* rowp = as + (r >> 3) * 1024 + (r & 7) * 128;
-                    const int sw = r & 7;
-                    *reinterpret_cast<uint4*>(rowp + (((2 * kq) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(rowp + (((2 * kq + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    for (int i = 0; i < CPT; i++) {
+                        const int c = t + GT_CONV_WARPS * 32 * i, r = c >> 2, kq = c & 3;
+                        const int4 v = *reinterpret_cast<const int4*>(qs + c * 16);
+                        const int w[4] = {v.x, v.y, v.z, v.w};
+                        uint32_t o[8];
+                        const Q8Scale qs2 = q8_scale_consts(sc[h][i]);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) q8_dequant4((uint32_t)w[j], qs2, o[2 * j], o[2 * j + 1]);
+                        unsigned char* rowp = as + (r >> 3) * 1024 + (r & 7) * 128;
+                        const int sw = r & 7;
+                        *reinterpret_cast<uint4*>(rowp + (((2 * kq) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(rowp + (((2 * kq + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
                 }
 #pragma unroll
-                for (int i = 0; i < CPT; i++) { sc[i] = sc1[i]; sc1[i] = sc2[i]; }
+                for (int h = 0; h < KH; h++)
+#pragma unroll
+                    for (int i = 0; i < CPT; i++) { sc[h][i] = sc1[h][i]; sc1[h][i] = sc2[h][i]; }
             } else if (WF == WF_MXFP4) {
                 // FP4_TPR threads share a row's 32 packed bytes; a 16-byte half of them is one scale block
                 const int r = t / FP4_TPR, part = t % FP4_TPR, hf = part / (FP4_TPR / 2), w0 = (part % (FP4_TPR / 2)) * FP4_WORDS;
@@ -417,11 +436,11 @@ __global__ void f32_to_out_kernel(const float* __restrict__ src, void* __restric
     }
 }
 
-template <int TN, typename TY, int WF>
+template <int TN, typename TY, int WF, int KH = 1>
 static int launch_tc(blum_ctx* ctx, const CUtensorMap& wmap, const CUtensorMap& xmap, const GemmTcParams& p, dim3 grid) {
-    auto kern = tc_gemm_kernel<TN, TY, WF>;
-    BLUM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GtCfg<TN, WF>::SMEM));
-    kern<<<grid, GT_THREADS, GtCfg<TN, WF>::SMEM, ctx->stream>>>(wmap, xmap, p);
+    auto kern = tc_gemm_kernel<TN, TY, WF, KH>;
+    BLUM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GtCfg<TN, WF, KH>::SMEM));
+    kern<<<grid, GT_THREADS, GtCfg<TN, WF, KH>::SMEM, ctx->stream>>>(wmap, xmap, p);
     BLUM_LAUNCH_CHECK(ctx);
     return BLUM_OK;
 }
@@ -449,7 +468,9 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     const int64_t mt = groups > 0 ? (rows_per_group_hint > 0 ? rows_per_group_hint : M) : M;
     const int TN = mt <= 32 ? 32 : mt <= 64 ? 64 : mt <= 128 ? 128 : 256;
     const int n_tiles = (N + GT_BN - 1) / GT_BN, m_tiles = (int)((M + TN - 1) / TN);
-    const int ksteps = K / GT_BK;
+    // small token tiles of the dense Q8_0 product take two 64-wide halves per stage (half as many hand-overs)
+    const int KH = (wf == WF_Q8_0 && groups == 0 && TN <= 64 && K % (2 * GT_BK) == 0) ? 2 : 1;
+    const int ksteps = K / (GT_BK * KH);
     int splits = 1;
     if (groups == 0) {
         // split K until the grid covers the SMs, keeping at least 8 stages per split
@@ -488,6 +509,10 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     }
     const dim3 grid(n_tiles, m_tiles, groups > 0 ? groups : splits);
     const bool f32_store = (ydt == BLUM_F32) || splits > 1;
+    if (KH == 2) {
+        rc = TN == 32 ? (f32_store ? launch_tc<32, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<32, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid))
+                      : (f32_store ? launch_tc<64, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<64, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid));
+    } else
     rc = wf == WF_Q8_0 ? launch_tc_tn<WF_Q8_0>(ctx, TN, f32_store, wmap, xmap, p, grid)
        : wf == WF_MXFP4 ? launch_tc_tn<WF_MXFP4>(ctx, TN, f32_store, wmap, xmap, p, grid)
                         : launch_tc_tn<WF_BF16>(ctx, TN, f32_store, wmap, xmap, p, grid);
