@@ -15,10 +15,15 @@
 //     tcgen05.commit frees the stage for the producer and finally signals the epilogue.
 //   * epilogue (warps 2-17): tcgen05.ld 32 lanes x 32 columns, convert, store y[m][n] (32 consecutive n per store).
 //   * split-K over CTAs (f32 atomics into a zeroed workspace) when there are too few tiles to fill the SMs.
-//   A variant with separate rings for raw weights, activations and dequantised tiles, dequantiser groups taking
-//   k-steps round robin and a single wait / commit per k-step in the MMA thread measured 8-13 % faster at M >= 512
-//   (917-952 TFLOP/s), but its N = 14336, M = 2048 launches ended in "unspecified launch failure" about once in a few
-//   hundred launches on part of the machines of the pool; the cause was not found and the variant is not used.
+//   What bounds it at small token tiles is the conversion itself: ~4.4 issued instructions per weight and CTA pass
+//   (prmt / fma.f32x2 / cvt per four weights plus per-chunk overhead), ~700 cycles per 64-wide k-step whatever the tile.
+//   Measured and dropped: a deep ring of raw int8 boxes (16 x 8 KB) beside a three-deep ring of converted tiles - slower
+//   (44 against 30 us on 4096 x 14336 at M = 64): the number of k-steps between conversion and MMA matters, not the bytes
+//   in flight; pulling later weight boxes into L2 with cp.async.bulk.prefetch.tensor - no change.  An earlier variant with
+//   separate rings and dequantiser groups ran 8-13 % faster at M >= 512 but ended in "unspecified launch failure" about
+//   once in a few hundred launches; reading it found a missing tcgen05.fence::after_thread_sync after a barrier wait, an
+//   activation tile the MMA thread never waited for itself, and a raw slot handed back to TMA without a proxy fence.
+//   It is not in the tree.
 // Every mbarrier wait is bounded: on expiry the CTA records an error word, stops issuing work and still frees its
 // TMEM.  No TMA load here uses cluster multicast.
 // Rounding: w = bf16(q*d) (8-bit significand), x bf16, f32 accumulation: ~1e-3 relative on y.  (Both MMA operands
