@@ -75,6 +75,10 @@ int blum_comm_selftest(int scenario, int timeout_ms, char* message_out, int mess
 /* Number of kernels launched by this library on ctx since creation (bench bookkeeping). */
 int64_t blum_launch_count(blum_ctx* ctx);
 
+/* Average device time of the packed-rows matmul (the integer-path kernel the decoder uses for 5 .. 128 rows) on one matrix:
+ * `copies` packed copies are cycled so that every launch streams from HBM; `iters` launches in one CUDA graph. */
+int blum_rows_matmul_timed(blum_ctx* ctx, const blum_q8_weight* w, int M, blum_dtype x_dtype, int copies, int iters, float* avg_us);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,5 +69,5 @@ int blum_ds_launch(blum_ctx* ctx, const DsParams& p);
 
 // prompt-chunk matmul over the same packed units (prefill_rows.cu)
 size_t blum_rows_scratch_bytes(int M, int64_t K_max, int64_t nk_max);
-int blum_rows_matmul(blum_ctx* ctx, const unsigned char* packed, int64_t rows_total, int64_t K, const float* x, int64_t ldx, int M,
-                     int swiglu, float* y, int64_t ldy, void* scratch, size_t scratch_bytes);
+int blum_rows_matmul(blum_ctx* ctx, const unsigned char* packed, int64_t rows_total, int64_t K, const void* x, int xdt, int64_t ldx, int M,
+                     int swiglu, void* y, int ydt, int64_t ldy, void* scratch, size_t scratch_bytes);

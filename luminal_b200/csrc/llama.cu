@@ -54,6 +54,7 @@ struct blum_llama {
     StreamPlan sp;
     int decode_path = 0;                          // 0: persistent stream kernel when the shape allows it, 1: per-op kernels in a CUDA graph
     int stream_state = -1;                        // -1 unknown, 0 unsupported, 1 supported
+    int pack_state = -1;                          // the same for the packed copy alone (the rows matmul)
     uint64_t weights_version = 1;
     int nq = 0, nkv = 0, ffn = 0, vocab = 0;      // local (tensor-parallel shard) sizes
     float* embed_f32 = nullptr;
@@ -123,15 +124,24 @@ static int pick_tokens(blum_ctx* ctx, blum_llama* m, int rows, const int32_t* se
 static bool stream_supported(blum_ctx* ctx, blum_llama* m);
 static int build_stream_plan(blum_ctx* ctx, blum_llama* m);
 
-// Rows of a prompt chunk in the f32 configuration: the projections read the stream-packed weights once per 32 rows
-// (prefill_rows.cu) instead of once per two rows through the GEMV.  Blocks of ROWS_BLOCK rows share one scratch area.
+static bool pack_supported(blum_ctx* ctx, blum_llama* m);
+static int ensure_packed(blum_ctx* ctx, blum_llama* m);
+
+// More than four rows of f32 activations (prompt chunks, small batches): the projections read the stream-packed weights once
+// per 32 rows on the integer tensor path (prefill_rows.cu).  Blocks of ROWS_BLOCK rows share one scratch area.  With 16-bit
+// activations the kernels that convert the weights are as fast or faster at these row counts (measured: 55 against 69 us
+// at 16 rows on 8192 x 28672) and need no second copy of the weights, so those models do not take this path.
 #define ROWS_BLOCK 128
-static int rows_mm(blum_ctx* ctx, blum_llama* m, int phase, const float* x, int64_t ldx, float* y, int64_t ldy, int R, int swiglu) {
+static int rows_mm(blum_ctx* ctx, blum_llama* m, int phase, const void* x, int64_t ldx, void* y, int64_t ldy, int R, int swiglu, int ydt = -1) {
     const DsPhase& P = m->sp.h_phases[(size_t)phase];
     const int64_t rows_total = (int64_t)P.groups * DS_UNIT_ROWS;
+    const int adt = m->cfg.act_dtype;
+    if (ydt < 0) ydt = adt;
+    const size_t xs = blum_dtype_size((blum_dtype)adt), ys = blum_dtype_size((blum_dtype)ydt);
     for (int r0 = 0; r0 < R; r0 += ROWS_BLOCK) {
         const int n = std::min(ROWS_BLOCK, R - r0);
-        TRY(blum_rows_matmul(ctx, P.w, rows_total, P.K, x + (int64_t)r0 * ldx, ldx, n, swiglu, y + (int64_t)r0 * ldy, ldy, m->rows_scratch, m->rows_scratch_bytes));
+        TRY(blum_rows_matmul(ctx, P.w, rows_total, P.K, (const char*)x + (size_t)r0 * ldx * xs, adt, ldx, n, swiglu,
+                             (char*)y + (size_t)r0 * ldy * ys, ydt, ldy, m->rows_scratch, m->rows_scratch_bytes));
     }
     return BLUM_OK;
 }
@@ -147,16 +157,9 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
     if (m->embed_q8) TRY(blum_q8_0_gather(ctx, m->embed_q8, ids, R, m->x, adt));
     else TRY(blum_gather(ctx, m->embed_f32, BLUM_F32, c.vocab, H, ids, R, m->x, adt));
     const bool fused = R <= GEMV_ROWS;
-    // more rows than the GEMV takes at once, f32 activations, and the model has (or can have) the stream-packed weights
-    const bool rows_path = !fused && adt == BLUM_F32 && m->decode_path == 0 && stream_supported(ctx, m);
-    if (rows_path) {
-        if (!m->sp.built || m->sp.weights_version != m->weights_version) TRY(build_stream_plan(ctx, m));
-        if (!m->rows_scratch) {
-            const int64_t nk = std::max<int64_t>((int64_t)(H / DS_UNIT_K) * 2 * m->ffn, (int64_t)(m->ffn / DS_UNIT_K) * H);
-            m->rows_scratch_bytes = blum_rows_scratch_bytes(ROWS_BLOCK, std::max(H, m->ffn), std::max<int64_t>(nk, (int64_t)(H / DS_UNIT_K) * (m->nq + 2 * m->nkv) * d));
-            BLUM_CUDA(ctx, cudaMalloc(&m->rows_scratch, m->rows_scratch_bytes));
-        }
-    }
+    // more rows than the GEMV takes at once and the model has (or can have) the stream-packed weights
+    const bool rows_path = !fused && m->decode_path == 0 && adt == BLUM_F32 && pack_supported(ctx, m);
+    if (rows_path) TRY(ensure_packed(ctx, m));
     // Programmatic dependent launch belongs to the fused GEMV chain, where every kernel lets its successor start early.
     // Outside it (row counts that take the GEMM kernels) the attribute buys nothing and is switched off.
     struct PdlGuard {
@@ -171,7 +174,7 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         } else {
             // (for l > 0 the previous layer's down-projection add already produced xn = rmsnorm(x) with this layer's weight)
             if (l == 0) TRY(blum_rmsnorm(ctx, m->x, nullptr, w.attn_norm, c.rms_eps, m->xn, nullptr, adt, R, H));
-            if (rows_path) TRY(rows_mm(ctx, m, 5 * l, (const float*)m->xn, H, (float*)m->qkv, (int64_t)(m->nq + 2 * m->nkv) * d, R, 0));
+            if (rows_path) TRY(rows_mm(ctx, m, 5 * l, m->xn, H, m->qkv, (int64_t)(m->nq + 2 * m->nkv) * d, R, 0));
             else TRY(blum_q8_0_matmul(ctx, w.wqkv, m->xn, adt, m->qkv, adt, R));
         }
         // The sibling decoders (per-head q/k norm, half-split rotary pairs) get their glue from one extra kernel that works in
@@ -226,7 +229,7 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         } else {
             // residual add and the following RMSNorm in one kernel: x <- x + proj (rounded as the separate add would),
             // xn <- rmsnorm(x) * weight.  The projection lands in the gate buffer, which is free here.
-            if (rows_path) TRY(rows_mm(ctx, m, 5 * l + 2, (const float*)m->attn, (int64_t)m->nq * d, (float*)m->gate, H, R, 0));
+            if (rows_path) TRY(rows_mm(ctx, m, 5 * l + 2, m->attn, (int64_t)m->nq * d, pull ? part0 : m->gate, H, R, 0));
             else TRY(blum_q8_0_matmul(ctx, w.wo, m->attn, adt, pull ? part0 : m->gate, adt, R));
             if (pull) {
                 TRY(blum_allreduce_fused(ctx, m->peer, 0, m->x, w.ffn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
@@ -235,8 +238,8 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
                 TRY(blum_rmsnorm(ctx, m->x, m->gate, w.ffn_norm, c.rms_eps, m->xn, m->x, adt, R, H));
             }
             if (rows_path) {
-                TRY(rows_mm(ctx, m, 5 * l + 3, (const float*)m->xn, H, (float*)m->mid, m->ffn, R, 1));       // SwiGLU in the finishing pass
-                TRY(rows_mm(ctx, m, 5 * l + 4, (const float*)m->mid, m->ffn, (float*)m->gate, H, R, 0));
+                TRY(rows_mm(ctx, m, 5 * l + 3, m->xn, H, m->mid, m->ffn, R, 1));       // SwiGLU in the finishing pass
+                TRY(rows_mm(ctx, m, 5 * l + 4, m->mid, m->ffn, pull ? part1 : m->gate, H, R, 0));
             } else {
                 TRY(blum_q8_0_matmul(ctx, w.wgate, m->xn, adt, m->gate, adt, R));
                 TRY(blum_q8_0_matmul(ctx, w.wup, m->xn, adt, m->up, adt, R));
@@ -261,7 +264,8 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
         TRY(blum_gemv_dispatch(ctx, m->head, nullptr, xh, adt, m->out_norm, c.rms_eps, nullptr, m->logits, BLUM_F32, HR));
     } else {
         TRY(blum_rmsnorm(ctx, xh, nullptr, m->out_norm, c.rms_eps, m->xn, nullptr, adt, HR, H));
-        TRY(blum_q8_0_matmul(ctx, m->head, m->xn, adt, m->logits, BLUM_F32, HR));
+        if (rows_path) TRY(rows_mm(ctx, m, 5 * c.layers, m->xn, H, m->logits, m->vocab, HR, 0, BLUM_F32));
+        else TRY(blum_q8_0_matmul(ctx, m->head, m->xn, adt, m->logits, BLUM_F32, HR));
     }
     if (c.tp_size > 1) {
         // vocabulary-parallel head: local (max, global index) per row, all-gather of the pairs, final pick
@@ -310,6 +314,43 @@ static void free_stream_plan(blum_llama* m) {
     for (void* b : bufs) if (b) cudaFree(b);
     sp.packed = nullptr; sp.d_phases = nullptr; sp.ctr = nullptr;
     sp.built = false;
+}
+
+static int build_stream_plan(blum_ctx* ctx, blum_llama* m);
+
+// The packed copy doubles the weight memory: models the persistent kernel covers always have it; others get it when their
+// shapes fit the 16 x 512 unit and the device has room for it beside what is already allocated.
+static bool pack_supported(blum_ctx* ctx, blum_llama* m) {
+    if (m->pack_state >= 0) return m->pack_state == 1;
+    bool ok = stream_supported(ctx, m);
+    if (!ok && m->cfg.act_dtype == BLUM_F32) {
+        const blum_llama_cfg& c = m->cfg;
+        const int d = c.head_dim, H = c.hidden;
+        const int64_t qkv_rows = (int64_t)(m->nq + 2 * m->nkv) * d, qd = (int64_t)m->nq * d;
+        ok = H % DS_UNIT_K == 0 && qd % DS_UNIT_K == 0 && m->ffn % DS_UNIT_K == 0 && 5 * c.layers + 1 <= DS_MAX_PHASES &&
+             qkv_rows % DS_UNIT_ROWS == 0 && H % DS_UNIT_ROWS == 0 && m->ffn % 8 == 0 && m->vocab % DS_UNIT_ROWS == 0 && m->head != nullptr;
+        if (ok) {
+            const size_t total = (blum_ds_packed_bytes(qkv_rows, H) + blum_ds_packed_bytes(H, qd) + blum_ds_packed_bytes(2ll * m->ffn, H) +
+                                  blum_ds_packed_bytes(H, m->ffn)) * (size_t)c.layers + blum_ds_packed_bytes(m->vocab, H);
+            size_t free_b = 0, total_b = 0;
+            ok = cudaMemGetInfo(&free_b, &total_b) == cudaSuccess && free_b > total + ((size_t)4 << 30);
+        }
+    }
+    m->pack_state = ok ? 1 : 0;
+    return ok;
+}
+// Everything the packed-rows matmul needs exists after this call (never inside a stream capture: it allocates).
+static int ensure_packed(blum_ctx* ctx, blum_llama* m) {
+    if (!m->sp.built || m->sp.weights_version != m->weights_version) TRY(build_stream_plan(ctx, m));
+    if (!m->rows_scratch) {
+        const int H = m->cfg.hidden, d = m->cfg.head_dim;
+        int64_t nk = std::max<int64_t>((int64_t)(H / DS_UNIT_K) * 2 * m->ffn, (int64_t)(m->ffn / DS_UNIT_K) * H);
+        nk = std::max<int64_t>(nk, (int64_t)(H / DS_UNIT_K) * (m->nq + 2 * m->nkv) * d);
+        nk = std::max<int64_t>(nk, (int64_t)(H / DS_UNIT_K) * m->vocab);
+        m->rows_scratch_bytes = blum_rows_scratch_bytes(ROWS_BLOCK, std::max<int64_t>(std::max(H, m->ffn), (int64_t)m->nq * d), nk);
+        BLUM_CUDA(ctx, cudaMalloc(&m->rows_scratch, m->rows_scratch_bytes));
+    }
+    return BLUM_OK;
 }
 
 // Packs every matrix of the model into stream units (once per set of weights) and writes the phase table.
@@ -410,6 +451,8 @@ static int run_stream_step(blum_ctx* ctx, blum_llama* m, int64_t max_ctx_len, in
 
 static int run_decode_step(blum_ctx* ctx, blum_llama* m, int R, int nsplit, int64_t max_ctx_len, int feed_step = -1, bool* fed = nullptr) {
     if (R == 1 && m->decode_path != 1 && stream_supported(ctx, m)) return run_stream_step(ctx, m, max_ctx_len, feed_step, fed);
+    if (R > GEMV_ROWS && m->decode_path == 0 && m->cfg.act_dtype == BLUM_F32 && pack_supported(ctx, m))
+        TRY(ensure_packed(ctx, m));          // allocations and packing happen outside the capture below
     auto key = std::make_pair(R, nsplit);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
@@ -575,7 +618,9 @@ int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out
     ALLOC(m->logits, (size_t)c.max_seqs * m->vocab * 4);
     {   // split-K workspace of the tensor-core GEMM for the widest projection, so that captured steps never allocate
         const int64_t widest = std::max<int64_t>((int64_t)(m->nq + 2 * m->nkv) * d, std::max<int64_t>(m->ffn, H));
-        if ((rc = blum_gemm_ws_reserve(ctx, (size_t)R * widest * sizeof(float)))) return fail(rc);
+        // (+ the digitised rows of the integer-path matmul: 32 rows of two byte planes and one scale per block)
+        const int64_t kmax = std::max<int64_t>((int64_t)m->nq * d, std::max<int64_t>(m->ffn, H));
+        if ((rc = blum_gemm_ws_reserve(ctx, (size_t)R * widest * sizeof(float) + (size_t)kmax * 72 + 4096))) return fail(rc);
     }
     ALLOC(m->d_rows, (size_t)4 * R * 4);
     ALLOC(m->d_next, (size_t)c.max_seqs * 4);
