@@ -34,23 +34,35 @@ __global__ void mxfp4_generate_kernel(uint8_t* __restrict__ q, uint8_t* __restri
         s[i] = (uint8_t)(119 + (((blum_gen_hash(key_s, (uint64_t)i) >> 32) * 9ull) >> 32));   // exponent uniform in [-8, 0]
 }
 
-// one CTA per token, 8 warps; warp w computes the logits of experts w, w+8, ...; warp 0 then selects
-__global__ void __launch_bounds__(256) moe_route_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
+// one CTA per token, 32 warps; warp w computes the logits of experts w, w+32, ... (all loads of a pass of 1024 columns in
+// flight together: at one token the kernel is nothing but load latency); warp 0 then selects
+#define MOE_ROUTE_WARPS 32
+__global__ void __launch_bounds__(32 * MOE_ROUTE_WARPS) moe_route_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
                                                         const float* __restrict__ bias, int H, int E, int k,
                                                         int32_t* __restrict__ ids, float* __restrict__ gates) {
     __shared__ float logits[256];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const __nv_bfloat16* xr = x + (size_t)t * H;
-    for (int e = warp; e < E; e += 8) {
+    for (int e = warp; e < E; e += MOE_ROUTE_WARPS) {
         const __nv_bfloat16* w = wr + (size_t)e * H;
         float acc = 0.f;
-        for (int h = lane * 8; h < H; h += 256) {
-            const uint4 a = *reinterpret_cast<const uint4*>(xr + h), b = *reinterpret_cast<const uint4*>(w + h);
-            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        for (int h0 = lane * 8; h0 < H; h0 += 1024) {
+            uint4 a[4], b[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                acc = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), acc);
-                acc = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), acc);
+            for (int u = 0; u < 4; u++) {
+                const int h = h0 + u * 256;
+                if (h < H) { a[u] = *reinterpret_cast<const uint4*>(xr + h); b[u] = *reinterpret_cast<const uint4*>(w + h); }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (h0 + u * 256 < H) {
+                    const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        acc = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), acc);
+                        acc = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), acc);
+                    }
+                }
             }
         }
         acc = warp_sum(acc);
@@ -124,11 +136,24 @@ template <typename TO>
 __global__ void moe_unpermute_kernel(const __nv_bfloat16* __restrict__ yp, const int32_t* __restrict__ slot_of,
                                      const float* __restrict__ gates, int k, int H, TO* __restrict__ out) {
     const int t = blockIdx.x;
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < k; j++)
-            acc = fmaf(gates[(size_t)t * k + j], __bfloat162float(yp[(size_t)slot_of[(size_t)t * k + j] * H + h]), acc);
-        out[(size_t)t * H + h] = from_f32<TO>(acc);
+    __shared__ float g_s[8];
+    __shared__ int slot_s[8];
+    if (threadIdx.x < k) { g_s[threadIdx.x] = gates[(size_t)t * k + threadIdx.x]; slot_s[threadIdx.x] = slot_of[(size_t)t * k + threadIdx.x]; }
+    __syncthreads();
+    // two columns per thread, the k rows of a column pair requested together (H is even)
+    for (int h = 2 * threadIdx.x; h < H; h += 2 * blockDim.x) {
+        uint32_t v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) if (j < k) v[j] = *reinterpret_cast<const uint32_t*>(yp + (size_t)slot_s[j] * H + h);
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (j < k) {
+                a0 = fmaf(g_s[j], __uint_as_float(v[j] << 16), a0);
+                a1 = fmaf(g_s[j], __uint_as_float(v[j] & 0xffff0000u), a1);
+            }
+        out[(size_t)t * H + h] = from_f32<TO>(a0);
+        out[(size_t)t * H + h + 1] = from_f32<TO>(a1);
     }
 }
 
@@ -203,7 +228,7 @@ int blum_moe_route_topk(blum_ctx* ctx, const void* x_bf16, const void* router_w_
     BLUM_REQUIRE(ctx, x_bf16 && router_w_bf16 && ids_out && gates_out, "moe_route: null argument");
     BLUM_REQUIRE(ctx, T >= 0 && H > 0 && H % 8 == 0 && E > 0 && E <= 256 && k > 0 && k <= 8 && k <= E, "moe_route: need H %% 8 == 0, E <= 256, k <= 8");
     if (T == 0) return BLUM_OK;
-    moe_route_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>((const __nv_bfloat16*)x_bf16, (const __nv_bfloat16*)router_w_bf16, router_bias,
+    moe_route_kernel<<<(unsigned)T, 32 * MOE_ROUTE_WARPS, 0, ctx->stream>>>((const __nv_bfloat16*)x_bf16, (const __nv_bfloat16*)router_w_bf16, router_bias,
                                                           H, E, k, ids_out, gates_out);
     BLUM_LAUNCH_CHECK(ctx);
     return BLUM_OK;
@@ -242,7 +267,7 @@ int blum_moe_grouped_gemm(blum_ctx* ctx, const blum_mxfp4_weight* w, const void*
 int blum_moe_unpermute(blum_ctx* ctx, const void* yp_bf16, const int32_t* slot_of, const float* gates, int64_t T, int k, int H,
                        void* out, blum_dtype out_dtype) {
     if (!ctx) return BLUM_ERR_INVALID;
-    BLUM_REQUIRE(ctx, yp_bf16 && slot_of && gates && out && k > 0 && H > 0, "moe_unpermute: bad argument");
+    BLUM_REQUIRE(ctx, yp_bf16 && slot_of && gates && out && k > 0 && k <= 8 && H > 0 && H % 2 == 0, "moe_unpermute: need k <= 8 and an even H");
     if (T == 0) return BLUM_OK;
     if (out_dtype == BLUM_F32) moe_unpermute_kernel<float><<<(unsigned)T, 256, 0, ctx->stream>>>((const __nv_bfloat16*)yp_bf16, slot_of, gates, k, H, (float*)out);
     else if (out_dtype == BLUM_BF16) moe_unpermute_kernel<__nv_bfloat16><<<(unsigned)T, 256, 0, ctx->stream>>>((const __nv_bfloat16*)yp_bf16, slot_of, gates, k, H, (__nv_bfloat16*)out);
