@@ -44,6 +44,8 @@ struct GemmTcParams {
     const void* scales;        // f16 [rows][K/32] (Q8_0) or e8m0 bytes [rows][K/32] (MXFP4); null for bf16 weights
     void* y;                   // [M][N] output, or f32 workspace when splits > 1
     const int* group_offsets;  // grouped mode: device [groups+1] row offsets into x / y; null for a dense product
+    const int* tile_list;      // grouped mode, optional: device [1 + 2 * max] = {count, (group, first row) ...}: blockIdx.y indexes
+                               // the token tiles that exist instead of (group, tile) pairs that mostly do not
     int N, K, M;
     int ksteps_per_split;      // 64-wide k stages per split
     int ksteps_total;
@@ -160,8 +162,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     // [group_offsets[g], group_offsets[g+1]) and its weights are rows [g*N, (g+1)*N) of the stacked weight tensor.
     int m0, m_end, wrow0, ks0, nk;
     if (p.group_offsets) {
-        const int g = blockIdx.z;
-        m0 = p.group_offsets[g] + blockIdx.y * TN;
+        int g = blockIdx.z;
+        if (p.tile_list) {
+            if ((int)blockIdx.y >= p.tile_list[0]) return;     // whole CTA: nothing allocated yet
+            g = p.tile_list[1 + 2 * blockIdx.y];
+            m0 = p.tile_list[2 + 2 * blockIdx.y];
+        } else {
+            m0 = p.group_offsets[g] + blockIdx.y * TN;
+        }
         m_end = p.group_offsets[g + 1];
         if (m0 >= m_end) return;                               // whole CTA: nothing allocated yet
         wrow0 = g * p.N;
@@ -434,6 +442,20 @@ int blum_tensor_map_2d(blum_ctx* ctx, void* map, int is_bf16, const void* base, 
                        base, inner, outer, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+// token tiles of a grouped product that exist: {count, (group, first row) ...}, groups in order (one CTA, thread per group)
+__global__ void group_tiles_kernel(const int* __restrict__ offsets, int groups, int tn, int* __restrict__ list) {
+    __shared__ int cnt[256];
+    const int g = threadIdx.x;
+    const int rows = g < groups ? offsets[g + 1] - offsets[g] : 0;
+    const int mine = (rows + tn - 1) / tn;
+    cnt[g] = mine;
+    __syncthreads();
+    int before = 0;
+    for (int i = 0; i < g; i++) before += cnt[i];
+    if (g < groups) for (int i = 0; i < mine; i++) { list[1 + 2 * (before + i)] = g; list[2 + 2 * (before + i)] = offsets[g] + i * tn; }
+    if (g == 255) list[0] = before + mine;
+}
+
 __global__ void f32_to_out_kernel(const float* __restrict__ src, void* __restrict__ dst, int64_t n, int dtype) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         if (dtype == BLUM_BF16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(src[i]);
@@ -512,7 +534,21 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
         BLUM_CUDA(ctx, cudaMemsetAsync(ws, 0, (size_t)M * N * sizeof(float), ctx->stream));
         p.y = ws;
     }
-    const dim3 grid(n_tiles, m_tiles, groups > 0 ? groups : splits);
+    dim3 grid(n_tiles, m_tiles, groups > 0 ? groups : splits);
+    p.tile_list = nullptr;
+    if (groups > 0 && groups <= 256) {
+        // every group has at most rows / TN + 1 token tiles: when that bound is well below groups x (tiles of all rows), the
+        // tiles that exist are listed on the device and the grid is sized by the bound
+        const int64_t bound = groups + M / TN;
+        if (bound * 2 < (int64_t)m_tiles * groups) {
+            const int wrc = blum_gemm_ws_reserve(ctx, (size_t)(1 + 2 * bound) * sizeof(int));
+            if (wrc) return wrc;
+            group_tiles_kernel<<<1, 256, 0, ctx->stream>>>(group_offsets, groups, TN, (int*)ctx->gemm_ws);
+            BLUM_LAUNCH_CHECK(ctx);
+            p.tile_list = (const int*)ctx->gemm_ws;
+            grid = dim3(n_tiles, (unsigned)bound, 1);
+        }
+    }
     const bool f32_store = (ydt == BLUM_F32) || splits > 1;
     if (KH == 2) {
         rc = TN == 32 ? (f32_store ? launch_tc<32, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<32, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid))
