@@ -409,6 +409,9 @@ def run_secondary(args, rank, world, local_rank):
     elif args.workload == "moe":
         if rank == 0:
             print(json.dumps(workloads.moe_layer(ctx, args.steps, args.warmup)), flush=True)
+    elif args.workload == "moe_stack":
+        if rank == 0:
+            print(json.dumps(workloads.moe_stack(ctx, args.steps, args.warmup, layers=args.layers, prompt=args.prompt or 128)), flush=True)
     else:   # tp70b / moe_ep: one process per GPU under torchrun; the NCCL id travels through a file next to the rendezvous port
         from luminal_b200.dist import Comm
         path = "/tmp/blum_nccl_id_%s" % os.environ.get("MASTER_PORT", "0")
@@ -440,7 +443,7 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel 70B record and its parity check")
-    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "serve64", "tp70b", "moe", "moe_ep", "sweep"],
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "serve64", "tp70b", "moe", "moe_stack", "moe_ep", "sweep"],
                     help="decode8b (default, the headline metric) or one of the secondary configurations")
     ap.add_argument("--layers", type=int, default=None, help="truncate the model to this many layers (small cases for profiler captures; the line says so)")
     ap.add_argument("--prompt", type=int, default=None, help="tp70b only: prompt length (default 1024)")

@@ -280,6 +280,14 @@ int blum_moe_gather_rows(blum_ctx* ctx, const void* x_bf16, const int32_t* sorte
                          void* xp_bf16);
 int blum_moe_grouped_gemm(blum_ctx* ctx, const blum_mxfp4_weight* w, const void* xp_bf16, const int32_t* offsets,
                           int64_t n_rows, void* yp, blum_dtype y_dtype, int rows_per_expert_hint);
+/* Gate and up matrices [E,I,K] as one weight [E,2I,K] whose rows alternate 16 gate rows and the 16 up rows of the same
+ * features (I % 16 == 0), the layout blum_moe_grouped_gemm_swiglu multiplies. */
+int blum_mxfp4_weight_stack_gate_up(blum_ctx* ctx, const blum_mxfp4_weight* gate, const blum_mxfp4_weight* up,
+                                    blum_mxfp4_weight** out);
+/* mid[r, :] = (xp[r,:] Wup_e^T) * swish(xp[r,:] Wgate_e^T) in ONE product over the stacked weight: gate and up sums stay
+ * f32 until the SwiGLU in the epilogue (the two-product form rounds both to bf16 first).  mid is bf16 [n_rows, I]. */
+int blum_moe_grouped_gemm_swiglu(blum_ctx* ctx, const blum_mxfp4_weight* w_gate_up, const void* xp_bf16,
+                                 const int32_t* offsets, int64_t n_rows, void* mid_bf16, int rows_per_expert_hint);
 int blum_moe_unpermute(blum_ctx* ctx, const void* yp_bf16, const int32_t* slot_of, const float* gates, int64_t T,
                        int k, int H, void* out, blum_dtype out_dtype);
 

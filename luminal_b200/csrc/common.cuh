@@ -10,6 +10,8 @@
 #include "../../include/blum.h"
 #include "../../include/blum_dev.h"
 
+#define BLUM_ARGMAX_ROWS 2048
+
 struct blum_ctx {
     int device = 0;
     int sm_count = 0;
@@ -29,6 +31,7 @@ struct blum_ctx {
     int trace_cap = 0, trace_next = 0;
     void* gemm_ws = nullptr;           // f32 workspace of the split-K tensor-core GEMM (grown on demand)
     size_t gemm_ws_bytes = 0;
+    void* argmax_ws = nullptr;         // BLUM_ARGMAX_ROWS zeroed 16-byte records of the split argmax (each launch leaves them zero)
     std::vector<void*> retired;        // outgrown workspaces: captured graphs may still name them, freed with the context
 };
 
@@ -46,6 +49,7 @@ struct blum_q8_weight {
 };
 
 int blum_fail(blum_ctx* ctx, int code, const char* fmt, ...);
+int blum_swiglu_rows(blum_ctx* ctx, const void* gate_up, void* out, int dt, int64_t R, int64_t F);
 
 #define BLUM_CUDA(ctx, call)                                                              \
     do {                                                                                  \
@@ -200,7 +204,7 @@ int blum_pick_pairs(blum_ctx* ctx, const int32_t* pairs, int nranks, int64_t row
 
 int blum_gemm_ws_reserve(blum_ctx* ctx, size_t bytes);
 int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, int64_t w_rows, int N, int K, const void* x,
-                 int64_t M, void* y, int ydt, const int* group_offsets, int groups, int rows_per_group_hint);
+                 int64_t M, void* y, int ydt, const int* group_offsets, int groups, int rows_per_group_hint, int swiglu = 0);
 
 // dispatch helpers -----------------------------------------------------------------------------
 #define BLUM_DISPATCH_DTYPE(dt, T, ...)                                  \

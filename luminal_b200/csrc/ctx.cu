@@ -36,6 +36,9 @@ int blum_ctx_create(int device, blum_ctx** out) {
     e = cudaMalloc(&ctx->dev_error, sizeof(int));
     if (e != cudaSuccess) { cudaStreamDestroy(ctx->stream); delete ctx; return BLUM_ERR_CUDA; }
     cudaMemset(ctx->dev_error, 0, sizeof(int));
+    e = cudaMalloc(&ctx->argmax_ws, (size_t)BLUM_ARGMAX_ROWS * 16);
+    if (e != cudaSuccess) { cudaFree(ctx->dev_error); cudaStreamDestroy(ctx->stream); delete ctx; return BLUM_ERR_CUDA; }
+    cudaMemset(ctx->argmax_ws, 0, (size_t)BLUM_ARGMAX_ROWS * 16);
     *out = ctx;
     return BLUM_OK;
 }
@@ -53,6 +56,7 @@ int blum_ctx_destroy(blum_ctx* ctx) {
     for (void* r : ctx->retired) cudaFree(r);
     if (ctx->trace) cudaFree(ctx->trace);
     if (ctx->dev_error) cudaFree(ctx->dev_error);
+    if (ctx->argmax_ws) cudaFree(ctx->argmax_ws);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return BLUM_OK;

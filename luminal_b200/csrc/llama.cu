@@ -28,6 +28,7 @@ struct LayerW {
     float* ffn_norm = nullptr;
     float *q_norm = nullptr, *k_norm = nullptr;     // per-head norm weights [head_dim] (qk_norm models)
     blum_q8_weight *wqkv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr, *wdown = nullptr;
+    blum_q8_weight* wgu = nullptr;     // gate rows then up rows in one allocation: wgate / wup are views of it
 };
 
 // The batch-1 step as one persistent kernel (decode_stream.cu): stream-packed copies of the weights, the phase table and
@@ -241,9 +242,8 @@ static int forward_rows(blum_ctx* ctx, blum_llama* m, int R, int nsplit, bool la
                 TRY(rows_mm(ctx, m, 5 * l + 3, m->xn, H, m->mid, m->ffn, R, 1));       // SwiGLU in the finishing pass
                 TRY(rows_mm(ctx, m, 5 * l + 4, m->mid, m->ffn, pull ? part1 : m->gate, H, R, 0));
             } else {
-                TRY(blum_q8_0_matmul(ctx, w.wgate, m->xn, adt, m->gate, adt, R));
-                TRY(blum_q8_0_matmul(ctx, w.wup, m->xn, adt, m->up, adt, R));
-                TRY(blum_swiglu(ctx, m->gate, m->up, m->mid, adt, (int64_t)R * m->ffn));
+                TRY(blum_q8_0_matmul(ctx, w.wgu, m->xn, adt, m->gate, adt, R));            // [R][gate | up]
+                TRY(blum_swiglu_rows(ctx, m->gate, m->mid, adt, R, m->ffn));
                 TRY(blum_q8_0_matmul(ctx, w.wdown, m->mid, adt, pull ? part1 : m->gate, adt, R));
             }
             if (pull) {
@@ -541,11 +541,11 @@ int blum_llama_destroy(blum_ctx* ctx, blum_llama* m) {
         if (w.q_norm) cudaFree(w.q_norm);
         if (w.k_norm) cudaFree(w.k_norm);
         blum_q8_0_weight_free(ctx, w.wqkv); blum_q8_0_weight_free(ctx, w.wo); blum_q8_0_weight_free(ctx, w.wgate);
-        blum_q8_0_weight_free(ctx, w.wup); blum_q8_0_weight_free(ctx, w.wdown);
+        blum_q8_0_weight_free(ctx, w.wup); blum_q8_0_weight_free(ctx, w.wdown); blum_q8_0_weight_free(ctx, w.wgu);
     }
     if (!m->cfg.tie_head) blum_q8_0_weight_free(ctx, m->head);
     blum_q8_0_weight_free(ctx, m->embed_q8);
-    void* bufs[] = {m->sample_scratch, m->rows_scratch, m->embed_f32, m->out_norm, m->x, m->xn, m->qkv, m->q, m->attn, m->mid, m->gate, m->up, m->logits,
+    void* bufs[] = {m->sample_scratch, m->rows_scratch, m->embed_f32, m->out_norm, m->x, m->xn, m->qkv, m->q, m->attn, m->mid, m->gate, m->logits,
                     m->d_rows, m->d_next, m->d_hist, m->attn_scratch, m->d_pairs};
     for (void* b : bufs) if (b) cudaFree(b);
     if (m->h_rows) cudaFreeHost(m->h_rows);
@@ -595,8 +595,12 @@ int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out
         if (c.qk_norm) { ALLOC(w.q_norm, (size_t)d * 4); ALLOC(w.k_norm, (size_t)d * 4); }
         if ((rc = blum_q8_alloc(ctx, (int64_t)(m->nq + 2 * m->nkv) * d, H, &w.wqkv))) return fail(rc);
         if ((rc = blum_q8_alloc(ctx, H, (int64_t)m->nq * d, &w.wo))) return fail(rc);
-        if ((rc = blum_q8_alloc(ctx, m->ffn, H, &w.wgate))) return fail(rc);
-        if ((rc = blum_q8_alloc(ctx, m->ffn, H, &w.wup))) return fail(rc);
+        // gate and up share one allocation so that the matrix kernels multiply both in one pass over x
+        if ((rc = blum_q8_alloc(ctx, 2ll * m->ffn, H, &w.wgu))) return fail(rc);
+        w.wgate = new blum_q8_weight(); w.wup = new blum_q8_weight();
+        w.wgate->N = w.wup->N = m->ffn; w.wgate->K = w.wup->K = H; w.wgate->owns = w.wup->owns = false;
+        w.wgate->q = w.wgu->q; w.wgate->d = w.wgu->d;
+        w.wup->q = w.wgu->q + (size_t)m->ffn * H; w.wup->d = w.wgu->d + (size_t)m->ffn * (H / 32);
         if ((rc = blum_q8_alloc(ctx, H, m->ffn, &w.wdown))) return fail(rc);
     }
     const int64_t per_layer = ((int64_t)(m->nq + 2 * m->nkv) * d * H + (int64_t)H * m->nq * d + 3ll * m->ffn * H);
@@ -613,11 +617,10 @@ int blum_llama_create(blum_ctx* ctx, const blum_llama_cfg* cfg, blum_llama** out
     ALLOC(m->q, act_bytes(m, (int64_t)R * m->nq * d));
     ALLOC(m->attn, act_bytes(m, (int64_t)R * m->nq * d));
     ALLOC(m->mid, act_bytes(m, (int64_t)R * m->ffn));
-    ALLOC(m->gate, act_bytes(m, (int64_t)R * std::max<int64_t>(m->ffn, H)));   // also takes the o / down projections before they join x
-    ALLOC(m->up, act_bytes(m, (int64_t)R * m->ffn));
+    ALLOC(m->gate, act_bytes(m, (int64_t)R * std::max<int64_t>(2ll * m->ffn, H)));   // [gate | up]; also takes the o / down projections before they join x
     ALLOC(m->logits, (size_t)c.max_seqs * m->vocab * 4);
     {   // split-K workspace of the tensor-core GEMM for the widest projection, so that captured steps never allocate
-        const int64_t widest = std::max<int64_t>((int64_t)(m->nq + 2 * m->nkv) * d, std::max<int64_t>(m->ffn, H));
+        const int64_t widest = std::max<int64_t>((int64_t)(m->nq + 2 * m->nkv) * d, std::max<int64_t>(2ll * m->ffn, H));
         // (+ the digitised rows of the integer-path matmul: 32 rows of two byte planes and one scale per block)
         const int64_t kmax = std::max<int64_t>((int64_t)m->nq * d, std::max<int64_t>(m->ffn, H));
         if ((rc = blum_gemm_ws_reserve(ctx, (size_t)R * widest * sizeof(float) + (size_t)kmax * 72 + 4096))) return fail(rc);

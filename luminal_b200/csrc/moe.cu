@@ -157,6 +157,18 @@ __global__ void moe_unpermute_kernel(const __nv_bfloat16* __restrict__ yp, const
     }
 }
 
+// rows of the stacked weight: 32-row groups, 16 gate rows then the 16 up rows of the same features; one 16-byte word per thread
+__global__ void mxfp4_stack_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, uint4* __restrict__ out, int64_t rows_out,
+                                   int64_t N, int words_per_row) {
+    const int64_t total = rows_out * words_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / words_per_row, w = i - r * words_per_row;
+        const int64_t e = r / (2 * N), rr = r - e * 2 * N;          // row inside the expert's 2N stacked rows
+        const int64_t src = e * N + (rr >> 5) * 16 + (rr & 15);
+        out[i] = ((rr & 16) ? u : g)[src * words_per_row + w];
+    }
+}
+
 extern "C" {
 
 int blum_mxfp4_weight_free(blum_ctx* ctx, blum_mxfp4_weight* w) {
@@ -213,6 +225,26 @@ int blum_mxfp4_weight_generate(blum_ctx* ctx, uint64_t seed, uint64_t tensor_id,
     return BLUM_OK;
 }
 
+int blum_mxfp4_weight_stack_gate_up(blum_ctx* ctx, const blum_mxfp4_weight* gate, const blum_mxfp4_weight* up, blum_mxfp4_weight** out) {
+    if (!ctx) return BLUM_ERR_INVALID;
+    BLUM_REQUIRE(ctx, gate && up && out, "mxfp4 stack: null argument");
+    BLUM_REQUIRE(ctx, gate->E == up->E && gate->N == up->N && gate->K == up->K, "mxfp4 stack: gate and up differ in shape");
+    BLUM_REQUIRE(ctx, gate->N % 16 == 0, "mxfp4 stack: need N %% 16 == 0");      // (K %% 64 == 0: a row's K/2 quant bytes are whole 16-byte words)
+    const int64_t N = gate->N, K = gate->K;
+    int rc = mxfp4_alloc(ctx, gate->E, 2 * N, K, out);
+    if (rc) return rc;
+    const int64_t rows_out = (int64_t)gate->E * 2 * N;
+    mxfp4_stack_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>((const uint4*)gate->q, (const uint4*)up->q, (uint4*)(*out)->q, rows_out, N, (int)(K / 32));
+    BLUM_LAUNCH_CHECK(ctx);
+    // the scale plane has K/32 bytes per row, not a multiple of 16 in general: it is copied 16 rows at a time as whole rows
+    BLUM_CUDA(ctx, cudaMemcpy2DAsync((*out)->s, (size_t)32 * (K / 32), gate->s, (size_t)16 * (K / 32), (size_t)16 * (K / 32), (size_t)(gate->E * N / 16),
+                                     cudaMemcpyDeviceToDevice, ctx->stream));
+    BLUM_CUDA(ctx, cudaMemcpy2DAsync((*out)->s + (size_t)16 * (K / 32), (size_t)32 * (K / 32), up->s, (size_t)16 * (K / 32), (size_t)16 * (K / 32),
+                                     (size_t)(gate->E * N / 16), cudaMemcpyDeviceToDevice, ctx->stream));
+    BLUM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return BLUM_OK;
+}
+
 int blum_mxfp4_weight_download(blum_ctx* ctx, const blum_mxfp4_weight* w, void* nibbles_out, void* scales_out) {
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, w && nibbles_out && scales_out, "mxfp4 download: null argument");
@@ -262,6 +294,16 @@ int blum_moe_grouped_gemm(blum_ctx* ctx, const blum_mxfp4_weight* w, const void*
     if (n_rows == 0) return BLUM_OK;
     return blum_tc_gemm(ctx, WF_MXFP4, w->q, w->s, (int64_t)w->E * w->N, (int)w->N, (int)w->K, xp_bf16, n_rows, yp, y_dtype,
                         offsets, w->E, rows_per_expert_hint);
+}
+
+int blum_moe_grouped_gemm_swiglu(blum_ctx* ctx, const blum_mxfp4_weight* w, const void* xp_bf16, const int32_t* offsets, int64_t n_rows,
+                                 void* mid_bf16, int rows_per_expert_hint) {
+    if (!ctx) return BLUM_ERR_INVALID;
+    BLUM_REQUIRE(ctx, w && xp_bf16 && offsets && mid_bf16, "moe_grouped_gemm_swiglu: null argument");
+    BLUM_REQUIRE(ctx, w->N % 32 == 0, "moe_grouped_gemm_swiglu: the weight is not a stacked gate/up weight");
+    if (n_rows == 0) return BLUM_OK;
+    return blum_tc_gemm(ctx, WF_MXFP4, w->q, w->s, (int64_t)w->E * w->N, (int)w->N, (int)w->K, xp_bf16, n_rows, mid_bf16, BLUM_BF16,
+                        offsets, w->E, rows_per_expert_hint, 1);
 }
 
 int blum_moe_unpermute(blum_ctx* ctx, const void* yp_bf16, const int32_t* slot_of, const float* gates, int64_t T, int k, int H,

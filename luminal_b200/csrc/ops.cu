@@ -168,6 +168,22 @@ void blum_rope_freqs(float theta, int head_dim, RopeFreqs* f) {
 }
 
 // ------------------------------------------------------------------ SwiGLU, add
+// rows of [gate | up] (2 F columns: one matmul over the stacked gate / up matrix) -> out [R][F]
+template <typename T>
+__global__ void swiglu_rows_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t R, int64_t F) {
+    constexpr int N = Vec16<T>::N;
+    const int64_t per_row = F / N, nv = R * per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nv; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / per_row, c = (i - r * per_row) * N;
+        float g[N], u[N], o[N];
+        load_vec<T>(gu + r * 2 * F + c, g);
+        load_vec<T>(gu + r * 2 * F + F + c, u);
+#pragma unroll
+        for (int j = 0; j < N; j++) o[j] = u[j] * (g[j] * (1.f / (1.f + expf(-g[j]))));
+        store_vec<T>(out + r * F + c, o);
+    }
+}
+
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t n) {
     constexpr int N = Vec16<T>::N;
@@ -276,6 +292,74 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ x, i
                 if (si[w] >= 0 && (bi < 0 || sv[w] > bv || (sv[w] == bv && si[w] > bi))) { bv = sv[w]; bi = si[w]; }
             }
             out[blockIdx.x] = bi;
+        }
+    }
+}
+
+// The same rule with a row split over several CTAs (a 128256-column row is 0.5 MB: one CTA per row reaches a fraction of
+// the memory rate).  Every CTA folds its part into a 64-bit key {order-preserving image of the value, index} and joins
+// it with atomicMax: the largest key is the last index holding the maximum.  The CTA that arrives last at the row's
+// counter writes the index and returns the row's scratch record to zero, so one launch does the whole job.
+// -0.0 enters as +0.0 (the two compare equal in the reference's fold); a row with a NaN is folded sequentially.
+struct ArgmaxRec { unsigned long long key; unsigned int nan, arrived; };
+
+__global__ void __launch_bounds__(512) argmax_split_kernel(const float* __restrict__ x, int64_t cols, int splits, ArgmaxRec* __restrict__ rec,
+                                                           int32_t* __restrict__ out) {
+    __shared__ unsigned long long sk[16];
+    __shared__ int snan;
+    const int row = blockIdx.x / splits, part = blockIdx.x - row * splits;
+    const float* xr = x + (size_t)row * cols;
+    // parts are whole float4 groups when the row allows it
+    const int64_t per = (((cols + splits - 1) / splits) + 3) & ~(int64_t)3;
+    const int64_t beg = per * part, end = min(cols, beg + per);
+    if (threadIdx.x == 0) snan = 0;
+    __syncthreads();
+    unsigned long long best = 0;
+    bool has_nan = false;
+    auto take = [&](float v, int64_t j) {
+        if (v != v) has_nan = true;
+        if (v == 0.f) v = 0.f;
+        const unsigned int b = __float_as_uint(v);
+        const unsigned long long k = ((unsigned long long)(b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u)) << 32) | (unsigned int)j;
+        best = k > best ? k : best;
+    };
+    if ((cols & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+        for (int64_t j = beg + 4 * (int64_t)threadIdx.x; j < end; j += 4 * (int64_t)blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + j);
+            take(v.x, j); take(v.y, j + 1); take(v.z, j + 2); take(v.w, j + 3);
+        }
+    } else {
+        for (int64_t j = beg + threadIdx.x; j < end; j += blockDim.x) take(xr[j], j);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
+        best = ok > best ? ok : best;
+    }
+    if (has_nan) snan = 1;
+    if ((threadIdx.x & 31) == 0) sk[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) best = sk[w] > best ? sk[w] : best;
+        ArgmaxRec* r = rec + row;
+        atomicMax(&r->key, best);
+        if (snan) atomicOr(&r->nan, 1u);
+        __threadfence();
+        if (atomicAdd(&r->arrived, 1u) == (unsigned)splits - 1) {
+            __threadfence();
+            const unsigned long long k = atomicMax(&r->key, 0ull);
+            int idx = (int)(unsigned int)k;
+            if (atomicOr(&r->nan, 0u)) {
+                float cur = xr[0]; idx = 0;
+                for (int64_t j = 1; j < cols; j++) {
+                    const float v = xr[j];
+                    if (!(cur > v)) { cur = v; idx = (int)j; }
+                }
+            }
+            out[row] = idx;
+            r->key = 0; r->nan = 0;
+            __threadfence();
+            r->arrived = 0;
         }
     }
 }
@@ -423,6 +507,16 @@ int blum_swiglu(blum_ctx* ctx, const void* gate, const void* up, void* out, blum
     return BLUM_OK;
 }
 
+}  // extern "C"
+int blum_swiglu_rows(blum_ctx* ctx, const void* gate_up, void* out, int dt, int64_t R, int64_t F) {
+    BLUM_REQUIRE(ctx, gate_up && out && R >= 0 && F > 0 && F % 8 == 0, "swiglu rows: bad argument");
+    if (R == 0) return BLUM_OK;
+    BLUM_DISPATCH_DTYPE(dt, T, (swiglu_rows_kernel<T><<<grid_for(ctx, R * F / 4 + 1, 256), 256, 0, ctx->stream>>>((const T*)gate_up, (T*)out, R, F)));
+    BLUM_LAUNCH_CHECK(ctx);
+    return BLUM_OK;
+}
+extern "C" {
+
 int blum_add(blum_ctx* ctx, const void* a, const void* b, void* out, blum_dtype dt, int64_t n) {
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, a && b && out && n >= 0, "add: bad argument");
@@ -445,6 +539,13 @@ int blum_argmax(blum_ctx* ctx, const void* logits, blum_dtype dt, int64_t rows, 
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, logits && out_idx && rows >= 0 && cols > 0 && cols < (1ll << 31), "argmax: bad argument");
     if (rows == 0) return BLUM_OK;
+    if (dt == BLUM_F32 && cols >= 8192 && rows <= BLUM_ARGMAX_ROWS && rows < 4 * (int64_t)ctx->sm_count) {
+        int splits = (int)((4 * (int64_t)ctx->sm_count + rows - 1) / rows);
+        splits = (int)std::min<int64_t>(splits, cols / 4096);
+        argmax_split_kernel<<<(unsigned)(rows * splits), 512, 0, ctx->stream>>>((const float*)logits, cols, splits, (ArgmaxRec*)ctx->argmax_ws, out_idx);
+        BLUM_LAUNCH_CHECK(ctx);
+        return BLUM_OK;
+    }
     BLUM_DISPATCH_DTYPE(dt, T, (argmax_kernel<T><<<(unsigned)rows, 1024, 0, ctx->stream>>>((const T*)logits, cols, out_idx)));
     BLUM_LAUNCH_CHECK(ctx);
     return BLUM_OK;

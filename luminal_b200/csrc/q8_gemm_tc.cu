@@ -50,6 +50,8 @@ struct GemmTcParams {
     int ksteps_per_split;      // 64-wide k stages per split
     int ksteps_total;
     int atomic_out;            // 1: atomicAdd f32 into y (split-K)
+    int swiglu;                // 1: weight rows alternate 16 gate / 16 up rows of the same 16 features; the epilogue pairs
+                               // them and stores silu(gate) * up into y [M][N/2] (no split-K in this mode)
     int* err;
 };
 
@@ -359,7 +361,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 uint32_t r[32];
                 tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.N) {
+                if (p.swiglu) {
+                    // lanes 0-15 hold the gate rows of 16 features, lanes 16-31 the up rows of the same features
+                    // (m, and with it every branch around the shuffle, is the same for the whole warp)
+                    const int f = ((n0 + quarter * 32) >> 1) + lane, F = p.N >> 1;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int m = m0 + c0 + j;
+                        if (m < m_end) {
+                            const float g = __uint_as_float(r[j]);
+                            const float u = __shfl_down_sync(0xffffffffu, g, 16);
+                            if (lane < 16 && f < F) reinterpret_cast<TY*>(p.y)[(size_t)m * F + f] = from_f32<TY>(u * (g * (1.f / (1.f + expf(-g)))));
+                        }
+                    }
+                } else if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int m = m0 + c0 + j;
@@ -486,8 +501,9 @@ static int launch_tc_tn(blum_ctx* ctx, int TN, bool f32_store, const CUtensorMap
 // groups == 0: dense, w_rows == N.  groups > 0: w_rows == groups*N, group_offsets is a device array [groups+1] of row
 // offsets into x / y (rows sorted by group).
 int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, int64_t w_rows, int N, int K, const void* x,
-                 int64_t M, void* y, int ydt, const int* group_offsets, int groups, int rows_per_group_hint) {
+                 int64_t M, void* y, int ydt, const int* group_offsets, int groups, int rows_per_group_hint, int swiglu) {
     BLUM_REQUIRE(ctx, wdata && x && y, "tc gemm: null argument");
+    BLUM_REQUIRE(ctx, !swiglu || (groups > 0 && N % 32 == 0), "tc gemm: the SwiGLU epilogue is built for grouped products with N %% 32 == 0");
     BLUM_REQUIRE(ctx, K % 64 == 0 && N > 0 && M > 0 && M < (1ll << 31), "tc gemm: need K %% 64 == 0 (K=%d), N>0, M>0", K);
     BLUM_REQUIRE(ctx, ydt == BLUM_BF16 || ydt == BLUM_F32, "tc gemm: output must be bf16 or f32");
     BLUM_REQUIRE(ctx, ((uintptr_t)x % 16) == 0 && ((uintptr_t)wdata % 16) == 0, "tc gemm: operands must be 16-byte aligned");
@@ -520,6 +536,7 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     p.ksteps_per_split = per_split; p.ksteps_total = ksteps;
     p.err = ctx->dev_error;
     p.atomic_out = splits > 1;
+    p.swiglu = swiglu;
     p.group_offsets = groups > 0 ? group_offsets : nullptr;
     p.y = y;
     float* ws = nullptr;

@@ -30,6 +30,13 @@ class Mxfp4Weight:
         ctx._check(ctx.lib.blum_mxfp4_weight_generate(ctx.h, seed, tensor_id, E, N, K, C.byref(h)))
         return cls(ctx, h.value, E, N, K)
 
+    @classmethod
+    def stack_gate_up(cls, gate, up):
+        """[E, 2N, K]: 16 gate rows, then the 16 up rows of the same features, and so on (the fused SwiGLU product's layout)."""
+        h = C.c_void_p()
+        gate.ctx._check(gate.ctx.lib.blum_mxfp4_weight_stack_gate_up(gate.ctx.h, gate.h, up.h, C.byref(h)))
+        return cls(gate.ctx, h.value, gate.E, 2 * gate.N, gate.K)
+
     def download(self):
         q = np.empty(self.E * self.N * self.K // 2, np.uint8)
         s = np.empty(self.E * self.N * self.K // 32, np.uint8)
@@ -49,10 +56,30 @@ class Mxfp4Weight:
 class MoeFfn:
     """One MoE feed-forward layer: bf16 router [E, H] (+ f32 bias), MXFP4 gate/up [E, I, H] and down [E, H, I]."""
 
-    def __init__(self, ctx: Context, hidden, inter, experts, top_k, router_w: DeviceBuffer, router_bias, w_gate, w_up, w_down):
+    def __init__(self, ctx: Context, hidden, inter, experts, top_k, router_w: DeviceBuffer, router_bias, w_gate, w_up, w_down,
+                 fused_swiglu=True, keep_separate=True):
+        """fused_swiglu: gate and up are multiplied as ONE grouped product over a stacked copy of the two weights, with the
+        SwiGLU in its epilogue (gate and up sums are then not rounded to bf16 before it).  keep_separate=False frees the two
+        separate weights once the stacked copy exists."""
         self.ctx, self.H, self.I, self.E, self.k = ctx, hidden, inter, experts, top_k
         self.router_w, self.router_bias = router_w, router_bias
         self.w_gate, self.w_up, self.w_down = w_gate, w_up, w_down
+        self.w_gate_up = None
+        if fused_swiglu and w_gate is not None and inter % 16 == 0:
+            self.w_gate_up = Mxfp4Weight.stack_gate_up(w_gate, w_up)
+            if not keep_separate:
+                w_gate.free()
+                w_up.free()
+                self.w_gate = self.w_up = None
+
+    def _gate_up_swiglu(self, xp, offsets, n, hint, g, u, mid):
+        ctx, lib = self.ctx, self.ctx.lib
+        if self.w_gate_up is not None:
+            ctx._check(lib.blum_moe_grouped_gemm_swiglu(ctx.h, self.w_gate_up.h, xp.ptr, offsets.ptr, n, mid.ptr, hint))
+            return
+        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_gate.h, xp.ptr, offsets.ptr, n, g.ptr, BF16, hint))
+        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_up.h, xp.ptr, offsets.ptr, n, u.ptr, BF16, hint))
+        ctx._check(lib.blum_swiglu(ctx.h, g.ptr, u.ptr, mid.ptr, BF16, n * self.I))
 
     def route(self, x: DeviceBuffer, T):
         ids, gates = self.ctx.alloc(max(T * self.k * 4, 16)), self.ctx.alloc(max(T * self.k * 4, 16))
@@ -72,7 +99,8 @@ class MoeFfn:
         ctx, n = self.ctx, T * self.k
         a = lambda nbytes: ctx.alloc(max(nbytes, 16))
         self._plan = dict(T=T, out_dtype=out_dtype, ids=a(n * 4), gates=a(n * 4), sorted_src=a(n * 4), slot_of=a(n * 4),
-                          offsets=a((self.E + 1) * 4), xp=a(n * self.H * 2), g=a(n * self.I * 2), u=a(n * self.I * 2),
+                          offsets=a((self.E + 1) * 4), xp=a(n * self.H * 2),
+                          g=a(n * self.I * 2) if self.w_gate_up is None else None, u=a(n * self.I * 2) if self.w_gate_up is None else None,
                           mid=a(n * self.I * 2), yp=a(n * self.H * 2), out=a(T * self.H * (4 if out_dtype == F32 else 2)))
         return self._plan
 
@@ -84,9 +112,7 @@ class MoeFfn:
                                            T, self.H, self.E, self.k, p["ids"].ptr, p["gates"].ptr))
         ctx._check(lib.blum_moe_permute(ctx.h, p["ids"].ptr, n, self.E, p["sorted_src"].ptr, p["slot_of"].ptr, p["offsets"].ptr))
         ctx._check(lib.blum_moe_gather_rows(ctx.h, x.ptr, p["sorted_src"].ptr, n, self.k, self.H, p["xp"].ptr))
-        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_gate.h, p["xp"].ptr, p["offsets"].ptr, n, p["g"].ptr, BF16, hint))
-        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_up.h, p["xp"].ptr, p["offsets"].ptr, n, p["u"].ptr, BF16, hint))
-        ctx._check(lib.blum_swiglu(ctx.h, p["g"].ptr, p["u"].ptr, p["mid"].ptr, BF16, n * self.I))
+        self._gate_up_swiglu(p["xp"], p["offsets"], n, hint, p["g"], p["u"], p["mid"])
         ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_down.h, p["mid"].ptr, p["offsets"].ptr, n, p["yp"].ptr, BF16, hint))
         ctx._check(lib.blum_moe_unpermute(ctx.h, p["yp"].ptr, p["slot_of"].ptr, p["gates"].ptr, T, self.k, self.H, p["out"].ptr, p["out_dtype"]))
         return p["out"]
@@ -99,11 +125,10 @@ class MoeFfn:
         xp = ctx.alloc(max(n * self.H * 2, 16))
         ctx._check(lib.blum_moe_gather_rows(ctx.h, x.ptr, sorted_src.ptr, n, self.k, self.H, xp.ptr))
         hint = max(1, n // self.E)
-        g, u = ctx.alloc(max(n * self.I * 2, 16)), ctx.alloc(max(n * self.I * 2, 16))
-        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_gate.h, xp.ptr, offsets.ptr, n, g.ptr, BF16, hint))
-        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_up.h, xp.ptr, offsets.ptr, n, u.ptr, BF16, hint))
+        sep = self.w_gate_up is None
+        g, u = (ctx.alloc(max(n * self.I * 2, 16)), ctx.alloc(max(n * self.I * 2, 16))) if sep else (None, None)
         mid = ctx.alloc(max(n * self.I * 2, 16))
-        ctx._check(lib.blum_swiglu(ctx.h, g.ptr, u.ptr, mid.ptr, BF16, n * self.I))
+        self._gate_up_swiglu(xp, offsets, n, hint, g, u, mid)
         yp = ctx.alloc(max(n * self.H * 2, 16))
         ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_down.h, mid.ptr, offsets.ptr, n, yp.ptr, BF16, hint))
         out = ctx.alloc(max(T * self.H * (4 if out_dtype == F32 else 2), 16))

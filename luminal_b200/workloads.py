@@ -198,6 +198,50 @@ def moe_layer(ctx: Context, steps, warmup, tokens=(1, 64, 1024), hidden=2880, in
             "per_batch": rows}
 
 
+def moe_stack(ctx: Context, steps, warmup, layers=None, batches=(1, 16, 64), prompt=128, seed=4):
+    """The whole MXFP4 mixture-of-experts decoder (24 layers of dense bf16 attention projections + the 32-expert top-4
+    feed-forward, luminal_b200/moe_model.py): a prompt pass per sequence, then decode steps replayed from a CUDA graph per
+    batch size.  The weight figure counts, per step, the dense projections once and the experts the step's tokens chose."""
+    from .moe_model import MOE_CFG, MoeDecoder
+    cfg = dict(MOE_CFG)
+    if layers:
+        cfg["layers"] = layers
+    B_max = max(batches)
+    model = MoeDecoder(ctx, cfg, max_seqs=B_max, max_ctx=prompt + 64, seed=seed)
+    seqs, toks = [], []
+    ctx.sync()
+    t0 = time.perf_counter()
+    for i in range(B_max):
+        s = model.new_sequence()
+        seqs.append(s)
+        toks.append(model.prefill(s, gen_token_ids(seed, 50 + i, prompt, cfg["vocab"])))
+    ctx.sync()
+    prefill_s = time.perf_counter() - t0
+    rows = []
+    for B in batches:
+        cur = list(toks[:B])
+        for _ in range(max(warmup, 3)):
+            cur = [int(t) for t in model.decode(seqs[:B], cur)]
+        g, nk = model.step_graph(B)
+        # timed: the captured step alone, replayed on fixed positions (the KV length does not grow inside the timed region)
+        ctx.timer_start(6)
+        for _ in range(steps):
+            ctx._check(ctx.lib.blum_graph_launch(ctx.h, g, nk))
+        ctx.timer_stop(6)
+        ms = ctx.timer_ms(6) / steps
+        hit = sum(len(set(w["ffn"]._plan["ids"].download(np.int32, B * model.k).tolist())) for w in model.layers)
+        expert_bytes = 3 * model.I * model.H * 17 // 32
+        dense = model.weight_bytes - model.L * 3 * model.E * expert_bytes
+        rows.append({"batch": B, "ms_per_step": ms, "tokens_per_s": B / (ms / 1e3), "kernels": nk, "experts_hit_per_layer": hit / model.L,
+                     "weight_GBps": (dense + hit * expert_bytes) / ms / 1e6})
+    ctx.check_device_error()
+    return {"metric": "moe_decode_tokens_per_s", "value": rows[-1]["tokens_per_s"], "unit": "tokens/s", "steps": steps, "dtype": "bf16",
+            "data": "synthetic", "truncated_layers": bool(layers),
+            "config": {"workload": "MXFP4 MoE decoder, %d layers, hidden %d, %d experts top-%d, prompt %d (seed %d)"
+                       % (cfg["layers"], cfg["hidden"], cfg["experts"], cfg["top_k"], prompt, seed)},
+            "prefill_tokens_per_s": B_max * prompt / prefill_s, "per_batch": rows}
+
+
 def moe_ep(ctx: Context, comm, rank, world, steps, warmup, tokens_per_rank=1024, hidden=2880, inter=2880, experts=32, top_k=4, seed=4):
     """The same MoE layer with the experts sharded over `world` GPUs and `tokens_per_rank` tokens owned by every rank
     (dispatch and combine through the NCCL all-to-all).  Each call crosses the host once (per-expert counts), so the

@@ -86,9 +86,11 @@ def swish(g):
     return g * (np.float32(1.0) / (np.float32(1.0) + np.exp(np.minimum(-g, np.float32(88.0)))))
 
 
-def moe_ffn_lazy(x, router_w, router_bias, expert, k):
+def moe_ffn_lazy(x, router_w, router_bias, expert, k, round_gate_up=True):
     """x [T,H] (bf16 values); expert(e) -> (wg [I,H], wu [I,H], wd [H,I]) as f32, called once per expert that is hit
-    (full-size layers hold gigabytes of dequantised weights otherwise).  Returns (out f32 [T,H], ids, gates)."""
+    (full-size layers hold gigabytes of dequantised weights otherwise).  Returns (out f32 [T,H], ids, gates).
+    round_gate_up: the gate and up products are stored as bf16 before the SwiGLU (the three-product form); False is the
+    one-product form, whose epilogue applies the SwiGLU to the f32 sums."""
     T = x.shape[0]
     ids, gates, _ = route(x, router_w, router_bias, k)
     out = np.zeros((T, x.shape[1]), np.float32)
@@ -96,8 +98,9 @@ def moe_ffn_lazy(x, router_w, router_bias, expert, k):
     for e in np.unique(ids):
         wg, wu, wd = expert(int(e))
         for t, j in zip(*np.nonzero(ids == e)):
-            g = round_bf16(wg @ x[t])
-            u = round_bf16(wu @ x[t])
+            g, u = wg @ x[t], wu @ x[t]
+            if round_gate_up:
+                g, u = round_bf16(g), round_bf16(u)
             mid = round_bf16(u * swish(g))
             contrib[t, j] = round_bf16(wd @ mid)
     for t in range(T):                       # the combine adds the k choices in choice order, in f32
@@ -106,6 +109,6 @@ def moe_ffn_lazy(x, router_w, router_bias, expert, k):
     return out, ids, gates
 
 
-def moe_ffn(x, router_w, router_bias, wg, wu, wd, k):
+def moe_ffn(x, router_w, router_bias, wg, wu, wd, k, round_gate_up=True):
     """x [T,H] (bf16 values); wg/wu f32 [E,I,H]; wd f32 [E,H,I] (already dequantised).  Returns (out f32 [T,H], ids, gates)."""
-    return moe_ffn_lazy(x, router_w, router_bias, lambda e: (wg[e], wu[e], wd[e]), k)
+    return moe_ffn_lazy(x, router_w, router_bias, lambda e: (wg[e], wu[e], wd[e]), k, round_gate_up)

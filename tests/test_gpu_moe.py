@@ -32,19 +32,36 @@ def test_mxfp4_generator_and_dequant_match_the_oracle(ctx):
     w.free()
 
 
+def test_stacked_gate_up_weight_layout(ctx):
+    """[E, 2N, K]: every 32 rows are 16 gate rows followed by the 16 up rows of the same features, quants and scales alike."""
+    E, N, K = 3, 48, 128
+    g, u = Mxfp4Weight.generate(ctx, 4, 930, E, N, K), Mxfp4Weight.generate(ctx, 4, 931, E, N, K)
+    st = Mxfp4Weight.stack_gate_up(g, u)
+    (gq, gs), (uq, us), (sq, ss) = g.download(), u.download(), st.download()
+    assert sq.shape == (E, 2 * N, K // 2) and ss.shape == (E, 2 * N, K // 32)
+    for got, a, b in ((sq, gq, uq), (ss, gs, us)):
+        got = got.reshape(E, N // 16, 2, 16, -1)
+        assert np.array_equal(got[:, :, 0], a.reshape(E, N // 16, 16, -1))
+        assert np.array_equal(got[:, :, 1], b.reshape(E, N // 16, 16, -1))
+    for w in (g, u, st):
+        w.free()
+
+
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("T", [1, 7, 64, 300])
-def test_moe_ffn_against_oracle(ctx, T):
+def test_moe_ffn_against_oracle(ctx, T, fused):
     H, I, E, k = 256, 384, 8, 2
     wg, wu, wd = (Mxfp4Weight.generate(ctx, 4, 910 + i, E, n, kk) for i, (n, kk) in enumerate(((I, H), (I, H), (H, I))))
     router = round_to_dtype(gen_normal(4, 920, E * H, 0.02).reshape(E, H), BF16)
     bias = (-1.1 * np.log(np.arange(1, E + 1))).astype(np.float32) * 0.05      # mild Zipf skew
     x = round_to_dtype(gen_normal(4, 921, T * H).reshape(T, H), BF16)
-    layer = MoeFfn(ctx, H, I, E, k, ctx.to_device(router, BF16), ctx.to_device(bias), wg, wu, wd)
+    layer = MoeFfn(ctx, H, I, E, k, ctx.to_device(router, BF16), ctx.to_device(bias), wg, wu, wd, fused_swiglu=fused)
+    assert (layer.w_gate_up is not None) == fused
     keep = {}
     out = ctx.to_host(layer.forward(ctx.to_device(x, BF16), T, out_dtype=F32, keep=keep), F32, T * H).reshape(T, H)
     ctx.check_device_error()
     deq = [omoe.dequant_mxfp4(*omoe.gen_mxfp4(4, 910 + i, E, n, kk)) for i, (n, kk) in enumerate(((I, H), (I, H), (H, I)))]
-    want, ids, gates = omoe.moe_ffn(x, router, bias, deq[0], deq[1], deq[2], k)
+    want, ids, gates = omoe.moe_ffn(x, router, bias, deq[0], deq[1], deq[2], k, round_gate_up=not fused)
     # routing and permutation are exact
     got_ids = keep["ids"].download(np.int32, T * k).reshape(T, k)
     assert np.array_equal(got_ids, ids)
@@ -57,12 +74,13 @@ def test_moe_ffn_against_oracle(ctx, T):
     scale = np.abs(want).max()
     assert_parity(out, want, max_abs=max(1e-2, 2e-2 * scale), rel=2e-2, what="moe ffn T=%d" % T)
     assert np.abs(out - want).mean() < 4e-3 * scale
-    for w in (wg, wu, wd):
+    for w in (wg, wu, wd) + ((layer.w_gate_up,) if fused else ()):
         w.free()
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("T", [1, 64])
-def test_moe_ffn_at_the_full_layer_size(ctx, T):
+def test_moe_ffn_at_the_full_layer_size(ctx, T, fused):
     """The MoE configuration's own dimensions (hidden = expert intermediate = 2880, 32 experts, top-4, Zipf-skewed router
     bias): routing and permutation exact, values at the contract tolerance.  The oracle dequantises only the experts that
     are hit, from the bytes the device holds; the device generator is checked against the oracle's on expert 0."""
@@ -74,12 +92,12 @@ def test_moe_ffn_at_the_full_layer_size(ctx, T):
     router = round_to_dtype(gen_normal(4, 950, E * H, 0.02).reshape(E, H), BF16)
     bias = (-1.1 * np.log(np.arange(1, E + 1))).astype(np.float32)              # expert load roughly Zipf(1.1)
     x = round_to_dtype(gen_normal(4, 951, T * H).reshape(T, H), BF16)
-    layer = MoeFfn(ctx, H, I, E, k, ctx.to_device(router, BF16), ctx.to_device(bias), *ws)
+    layer = MoeFfn(ctx, H, I, E, k, ctx.to_device(router, BF16), ctx.to_device(bias), *ws, fused_swiglu=fused)
     keep = {}
     out = ctx.to_host(layer.forward(ctx.to_device(x, BF16), T, out_dtype=F32, keep=keep), F32, T * H).reshape(T, H)
     ctx.check_device_error()
     expert = lambda e: tuple(omoe.dequant_mxfp4(q[e], s[e]) for q, s in host)
-    want, ids, gates = omoe.moe_ffn_lazy(x, router, bias, expert, k)
+    want, ids, gates = omoe.moe_ffn_lazy(x, router, bias, expert, k, round_gate_up=not fused)
     assert np.array_equal(keep["ids"].download(np.int32, T * k).reshape(T, k), ids)
     assert np.abs(ctx.to_host(keep["gates"], F32, T * k).reshape(T, k) - gates).max() < 1e-5
     ss, so, off = omoe.permute(ids, E)
@@ -89,7 +107,7 @@ def test_moe_ffn_at_the_full_layer_size(ctx, T):
     scale = np.abs(want).max()
     assert_parity(out, want, max_abs=max(1e-2, 2e-2 * scale), rel=2e-2, what="moe ffn 2880/32/top-4 T=%d" % T)
     assert np.abs(out - want).mean() < 4e-3 * scale
-    for w in ws:
+    for w in ws + ([layer.w_gate_up] if fused else []):
         w.free()
 
 

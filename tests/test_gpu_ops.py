@@ -124,3 +124,25 @@ def test_argmax_greedy_rule(ctx, orc):
     assert ops.argmax(ctx, ctx.to_device(v), 1, 128256)[0] == 128255 == orc.argmax(v)
     m = gen_normal(3, 2, 3 * 1000).reshape(3, 1000)
     assert ops.argmax(ctx, ctx.to_device(m), 3, 1000).tolist() == [orc.argmax(r) for r in m]
+
+
+def test_argmax_rows_split_over_several_ctas(ctx, orc):
+    """Wide f32 rows are split over CTAs that join 64-bit {value, index} keys: ties across parts, signed zeros, -inf rows,
+    NaN rows, odd widths (the scalar-load form), and a second call on the same context (the records return to zero)."""
+    for cols in (128256, 32768, 9001):
+        m = gen_normal(3, 40 + cols % 7, 6 * cols).reshape(6, cols)
+        m[0, [3, cols // 2, cols - 2]] = 11.0                       # equal maxima in different parts: the last one
+        m[1, :] = -np.inf                                           # every element equal: the last index
+        m[2, :] = -1.0
+        m[2, [17, cols - 100]] = [0.0, -0.0]                        # +0 then -0 compare equal: the later index
+        m[3, [5, cols - 9]] = [-0.0, 0.0]
+        m[3, m[3] > 0] = -1.0
+        m[4, cols // 3] = np.nan                                    # the sequential fold of the reference
+        want = [orc.argmax(r) for r in m]
+        assert want[0] == cols - 2 and want[1] == cols - 1 and want[2] == cols - 100 and want[3] == cols - 9
+        d = ctx.to_device(m)
+        for _ in range(2):
+            assert ops.argmax(ctx, d, 6, cols).tolist() == want, cols
+    one = gen_normal(3, 77, 128256)
+    assert ops.argmax(ctx, ctx.to_device(one), 1, 128256)[0] == orc.argmax(one)
+    ctx.check_device_error()
