@@ -288,6 +288,15 @@ int blum_mxfp4_weight_stack_gate_up(blum_ctx* ctx, const blum_mxfp4_weight* gate
  * f32 until the SwiGLU in the epilogue (the two-product form rounds both to bf16 first).  mid is bf16 [n_rows, I]. */
 int blum_moe_grouped_gemm_swiglu(blum_ctx* ctx, const blum_mxfp4_weight* w_gate_up, const void* xp_bf16,
                                  const int32_t* offsets, int64_t n_rows, void* mid_bf16, int rows_per_expert_hint);
+/* The expert half of the layer for small row counts (decode steps), in a streaming kernel without tensor-memory
+ * hand-overs, from the rows sorted by expert to the gate-weighted sum of each token's k choices: two products (gate/up
+ * over the stacked weight, SwiGLU applied while the second product stages its input, down) and the combine.  Numerics as
+ * the tensor-core path with the SwiGLU epilogue: f32 gate/up sums, mid and down rows rounded to bf16.  Workspace comes
+ * from the context (blum_moe_experts_small_ws_bytes; reserved on the first call, which must not be a captured one). */
+int64_t blum_moe_experts_small_ws_bytes(int E, int64_t n_rows, int64_t inter, int64_t hidden);
+int blum_moe_experts_small(blum_ctx* ctx, const blum_mxfp4_weight* w_gate_up, const blum_mxfp4_weight* w_down,
+                           const void* xp_bf16, const int32_t* offsets, int64_t n_rows, const int32_t* slot_of,
+                           const float* gates, int64_t T, int k, void* out, blum_dtype out_dtype);
 int blum_moe_unpermute(blum_ctx* ctx, const void* yp_bf16, const int32_t* slot_of, const float* gates, int64_t T,
                        int k, int H, void* out, blum_dtype out_dtype);
 

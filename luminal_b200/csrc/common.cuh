@@ -48,6 +48,13 @@ struct blum_q8_weight {
     bool owns = true;
 };
 
+struct blum_mxfp4_weight {
+    int E = 0;
+    int64_t N = 0, K = 0;
+    uint8_t* q = nullptr;      // [E*N][K/2] packed e2m1
+    uint8_t* s = nullptr;      // [E*N][K/32] e8m0
+};
+
 int blum_fail(blum_ctx* ctx, int code, const char* fmt, ...);
 int blum_swiglu_rows(blum_ctx* ctx, const void* gate_up, void* out, int dt, int64_t R, int64_t F);
 

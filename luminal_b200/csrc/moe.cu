@@ -13,12 +13,6 @@
 #include "common.cuh"
 #include <string.h>
 
-struct blum_mxfp4_weight {
-    int E = 0;
-    int64_t N = 0, K = 0;
-    uint8_t* q = nullptr;      // [E*N][K/2] packed e2m1
-    uint8_t* s = nullptr;      // [E*N][K/32] e8m0
-};
 
 enum { WF_Q8_0 = 0, WF_MXFP4 = 1, WF_BF16 = 2 };
 
@@ -96,28 +90,42 @@ __global__ void __launch_bounds__(32 * MOE_ROUTE_WARPS) moe_route_kernel(const _
     }
 }
 
-// Stable counting sort of the T*k (token, choice) pairs by expert: one CTA, thread e owns expert e.
-__global__ void moe_permute_kernel(const int32_t* __restrict__ ids, int n, int E, int32_t* __restrict__ sorted_src,
-                                   int32_t* __restrict__ slot_of, int32_t* __restrict__ offsets, int* err) {
+// Stable counting sort of the T*k (token, choice) pairs by expert: one CTA of 32 warps, a warp per expert (round-robin when
+// there are more than 32).  A warp reads 32 pairs per step; the ballot of "this pair chose my expert" gives the count in the
+// first pass and, with the prefix of lower lanes, each pair's sorted row in the second - pair order inside an expert is kept.
+__global__ void __launch_bounds__(1024) moe_permute_kernel(const int32_t* __restrict__ ids, int n, int E, int32_t* __restrict__ sorted_src,
+                                                           int32_t* __restrict__ slot_of, int32_t* __restrict__ offsets, int* err) {
     __shared__ int counts[257];
-    const int e = threadIdx.x;
-    if (e < E) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += warps) {
         int c = 0;
-        for (int i = 0; i < n; i++) c += (ids[i] == e);
-        counts[e] = c;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            c += __popc(__ballot_sync(0xffffffffu, i < n && ids[i] == e));
+        }
+        if (lane == 0) counts[e] = c;
     }
     __syncthreads();
-    if (e == 0) {
+    if (threadIdx.x == 0) {
         int run = 0;
         for (int j = 0; j < E; j++) { const int c = counts[j]; counts[j] = run; offsets[j] = run; run += c; }
         offsets[E] = run;
         if (run != n) atomicOr(err, 0x2000);       // an expert id outside [0,E)
     }
     __syncthreads();
-    if (e < E) {
+    for (int e = warp; e < E; e += warps) {
         int pos = counts[e];
-        for (int i = 0; i < n; i++)
-            if (ids[i] == e) { sorted_src[pos] = i; slot_of[i] = pos; pos++; }
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool mine = i < n && ids[i] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int r = pos + __popc(m & ((1u << lane) - 1u));
+                sorted_src[r] = i;
+                slot_of[i] = r;
+            }
+            pos += __popc(m);
+        }
     }
 }
 
@@ -272,7 +280,7 @@ int blum_moe_permute(blum_ctx* ctx, const int32_t* ids, int64_t n_pairs, int E, 
                      int32_t* offsets) {
     if (!ctx) return BLUM_ERR_INVALID;
     BLUM_REQUIRE(ctx, ids && sorted_src && slot_of && offsets && n_pairs >= 0 && E > 0 && E <= 256, "moe_permute: bad argument");
-    moe_permute_kernel<<<1, 256, 0, ctx->stream>>>(ids, (int)n_pairs, E, sorted_src, slot_of, offsets, ctx->dev_error);
+    moe_permute_kernel<<<1, 1024, 0, ctx->stream>>>(ids, (int)n_pairs, E, sorted_src, slot_of, offsets, ctx->dev_error);
     BLUM_LAUNCH_CHECK(ctx);
     return BLUM_OK;
 }

@@ -126,14 +126,15 @@ enum { WF_Q8_0 = 0, WF_MXFP4 = 1, WF_BF16 = 2 };
 
 // KH: 64-wide k halves per pipeline stage.  One stage is one hand-over (barrier wait, MMA issue, commit) whatever it holds, and
 // at small token tiles that fixed cost, not the tensor work, sets the pace: two halves per stage halve the hand-overs.
-template <int TN, int WF, int KH = 1> struct GtCfg {
+// CPS: CTAs meant to share an SM (the ring gets 1/CPS of the shared memory)
+template <int TN, int WF, int KH = 1, int CPS = 1> struct GtCfg {
     static constexpr int A_BYTES = GT_BN * GT_BK * 2;       // 16384, bf16 weights in UMMA layout
     static constexpr int X_BYTES = TN * GT_BK * 2;          // bf16 activations
     // raw weight staging per stage: int8 [128][64], packed e2m1 nibbles [128][32], or none (bf16 lands in A directly)
     static constexpr int Q_BYTES = WF == WF_Q8_0 ? GT_BN * GT_BK : WF == WF_MXFP4 ? GT_BN * GT_BK / 2 : 0;
     static constexpr int HALF_BYTES = A_BYTES + X_BYTES + Q_BYTES;
     static constexpr int STAGE_BYTES = KH * HALF_BYTES;
-    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = (200 * 1024 / CPS) / STAGE_BYTES > 8 ? 8 : (200 * 1024 / CPS) / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;   // + alignment slack
     static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
     static constexpr int TX_BYTES = KH * ((WF == WF_BF16 ? A_BYTES : Q_BYTES) + X_BYTES);
@@ -146,10 +147,11 @@ __device__ __forceinline__ float e2m1_value(int code) {
     return (code & 8) ? -mag : mag;
 }
 
-template <int TN, typename TY, int WF, int KH>
-__global__ void __launch_bounds__(GT_THREADS, 1)
+template <int TN, typename TY, int WF, int KH, int CPS>
+__global__ void __launch_bounds__(GT_THREADS, CPS)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, const GemmTcParams p) {
-    using C = GtCfg<TN, WF, KH>;
+    using C = GtCfg<TN, WF, KH, CPS>;
+    static_assert(C::STAGES >= 2 && CPS * C::TMEM_COLS <= 512, "ring or tensor memory does not fit this many CTAs per SM");
     static_assert(KH == 1 || WF == WF_Q8_0, "two halves per stage are built for Q8_0 weights only");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -478,13 +480,24 @@ __global__ void f32_to_out_kernel(const float* __restrict__ src, void* __restric
     }
 }
 
-template <int TN, typename TY, int WF, int KH = 1>
+template <int TN, typename TY, int WF, int KH = 1, int CPS = 1>
 static int launch_tc(blum_ctx* ctx, const CUtensorMap& wmap, const CUtensorMap& xmap, const GemmTcParams& p, dim3 grid) {
-    auto kern = tc_gemm_kernel<TN, TY, WF, KH>;
-    BLUM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GtCfg<TN, WF, KH>::SMEM));
-    kern<<<grid, GT_THREADS, GtCfg<TN, WF, KH>::SMEM, ctx->stream>>>(wmap, xmap, p);
+    auto kern = tc_gemm_kernel<TN, TY, WF, KH, CPS>;
+    BLUM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GtCfg<TN, WF, KH, CPS>::SMEM));
+    kern<<<grid, GT_THREADS, GtCfg<TN, WF, KH, CPS>::SMEM, ctx->stream>>>(wmap, xmap, p);
     BLUM_LAUNCH_CHECK(ctx);
     return BLUM_OK;
+}
+
+// Grouped MXFP4 products with token tiles of up to 64 rows run two CTAs per SM (half the ring each): with a few rows per
+// expert the k-step chain of one CTA leaves the SM idle most of the time (MoE layer at 64 tokens 421 -> 364 us, at 256
+// tokens 791 -> 652 us).  The dense Q8_0 product keeps one CTA with two 64-wide halves per stage (28 us against 38 us
+// for the pair on 4096 x 14336 at 64 rows).
+template <int WF>
+static int launch_tc_pair(blum_ctx* ctx, int TN, bool f32_store, const CUtensorMap& wmap, const CUtensorMap& xmap, const GemmTcParams& p, dim3 grid) {
+#define TC2(tn) (f32_store ? launch_tc<tn, float, WF, 1, 2>(ctx, wmap, xmap, p, grid) : launch_tc<tn, __nv_bfloat16, WF, 1, 2>(ctx, wmap, xmap, p, grid))
+    return TN == 32 ? TC2(32) : TC2(64);
+#undef TC2
 }
 
 template <int WF>
@@ -512,7 +525,8 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     const int TN = mt <= 32 ? 32 : mt <= 64 ? 64 : mt <= 128 ? 128 : 256;
     const int n_tiles = (N + GT_BN - 1) / GT_BN, m_tiles = (int)((M + TN - 1) / TN);
     // small token tiles of the dense Q8_0 product take two 64-wide halves per stage (half as many hand-overs)
-    const int KH = (wf == WF_Q8_0 && groups == 0 && TN <= 64 && K % (2 * GT_BK) == 0) ? 2 : 1;
+    const bool pair = wf == WF_MXFP4 && groups > 0 && TN <= 64;
+    const int KH = (!pair && wf == WF_Q8_0 && groups == 0 && TN <= 64 && K % (2 * GT_BK) == 0) ? 2 : 1;
     const int ksteps = K / (GT_BK * KH);
     int splits = 1;
     if (groups == 0) {
@@ -570,7 +584,9 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     if (KH == 2) {
         rc = TN == 32 ? (f32_store ? launch_tc<32, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<32, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid))
                       : (f32_store ? launch_tc<64, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<64, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid));
-    } else
+    } else if (pair)
+        rc = launch_tc_pair<WF_MXFP4>(ctx, TN, f32_store, wmap, xmap, p, grid);
+    else
     rc = wf == WF_Q8_0 ? launch_tc_tn<WF_Q8_0>(ctx, TN, f32_store, wmap, xmap, p, grid)
        : wf == WF_MXFP4 ? launch_tc_tn<WF_MXFP4>(ctx, TN, f32_store, wmap, xmap, p, grid)
                         : launch_tc_tn<WF_BF16>(ctx, TN, f32_store, wmap, xmap, p, grid);

@@ -72,6 +72,24 @@ class MoeFfn:
                 w_up.free()
                 self.w_gate = self.w_up = None
 
+    # rows (token, choice pairs) up to which the streaming kernel (csrc/moe_small.cu) runs both expert products; above it the
+    # tcgen05 grouped GEMMs do
+    SMALL_ROWS = 1024
+
+    def _small(self, n):
+        return self.w_gate_up is not None and n <= self.SMALL_ROWS and self.H % 32 == 0 and self.I % 32 == 0
+
+    def _experts(self, xp, offsets, n, hint, g, u, mid, yp, slot_of, gates, T, out, out_dtype):
+        """From the rows sorted by expert to the layer output: SwiGLU of the gate / up products, down product, combine."""
+        ctx, lib = self.ctx, self.ctx.lib
+        if self._small(n):
+            ctx._check(lib.blum_moe_experts_small(ctx.h, self.w_gate_up.h, self.w_down.h, xp.ptr, offsets.ptr, n, slot_of.ptr, gates.ptr,
+                                                  T, self.k, out.ptr, out_dtype))
+            return
+        self._gate_up_swiglu(xp, offsets, n, hint, g, u, mid)
+        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_down.h, mid.ptr, offsets.ptr, n, yp.ptr, BF16, hint))
+        ctx._check(lib.blum_moe_unpermute(ctx.h, yp.ptr, slot_of.ptr, gates.ptr, T, self.k, self.H, out.ptr, out_dtype))
+
     def _gate_up_swiglu(self, xp, offsets, n, hint, g, u, mid):
         ctx, lib = self.ctx, self.ctx.lib
         if self.w_gate_up is not None:
@@ -112,9 +130,7 @@ class MoeFfn:
                                            T, self.H, self.E, self.k, p["ids"].ptr, p["gates"].ptr))
         ctx._check(lib.blum_moe_permute(ctx.h, p["ids"].ptr, n, self.E, p["sorted_src"].ptr, p["slot_of"].ptr, p["offsets"].ptr))
         ctx._check(lib.blum_moe_gather_rows(ctx.h, x.ptr, p["sorted_src"].ptr, n, self.k, self.H, p["xp"].ptr))
-        self._gate_up_swiglu(p["xp"], p["offsets"], n, hint, p["g"], p["u"], p["mid"])
-        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_down.h, p["mid"].ptr, p["offsets"].ptr, n, p["yp"].ptr, BF16, hint))
-        ctx._check(lib.blum_moe_unpermute(ctx.h, p["yp"].ptr, p["slot_of"].ptr, p["gates"].ptr, T, self.k, self.H, p["out"].ptr, p["out_dtype"]))
+        self._experts(p["xp"], p["offsets"], n, hint, p["g"], p["u"], p["mid"], p["yp"], p["slot_of"], p["gates"], T, p["out"], p["out_dtype"])
         return p["out"]
 
     def forward(self, x: DeviceBuffer, T, out_dtype=BF16, keep=None):
@@ -128,11 +144,9 @@ class MoeFfn:
         sep = self.w_gate_up is None
         g, u = (ctx.alloc(max(n * self.I * 2, 16)), ctx.alloc(max(n * self.I * 2, 16))) if sep else (None, None)
         mid = ctx.alloc(max(n * self.I * 2, 16))
-        self._gate_up_swiglu(xp, offsets, n, hint, g, u, mid)
         yp = ctx.alloc(max(n * self.H * 2, 16))
-        ctx._check(lib.blum_moe_grouped_gemm(ctx.h, self.w_down.h, mid.ptr, offsets.ptr, n, yp.ptr, BF16, hint))
         out = ctx.alloc(max(T * self.H * (4 if out_dtype == F32 else 2), 16))
-        ctx._check(lib.blum_moe_unpermute(ctx.h, yp.ptr, slot_of.ptr, gates.ptr, T, self.k, self.H, out.ptr, out_dtype))
+        self._experts(xp, offsets, n, hint, g, u, mid, yp, slot_of, gates, T, out, out_dtype)
         ctx.sync()
         if keep is not None:
             keep.update(ids=ids, gates=gates, sorted_src=sorted_src, slot_of=slot_of, offsets=offsets, xp=xp, yp=yp)

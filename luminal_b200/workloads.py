@@ -230,8 +230,8 @@ def moe_stack(ctx: Context, steps, warmup, layers=None, batches=(1, 16, 64), pro
         ctx.timer_stop(6)
         ms = ctx.timer_ms(6) / steps
         hit = sum(len(set(w["ffn"]._plan["ids"].download(np.int32, B * model.k).tolist())) for w in model.layers)
-        expert_bytes = 3 * model.I * model.H * 17 // 32
-        dense = model.weight_bytes - model.L * 3 * model.E * expert_bytes
+        expert_bytes = 3 * model.I * model.H * 17 // 32                   # one expert's gate, up and down matrices
+        dense = model.weight_bytes - model.L * model.E * expert_bytes
         rows.append({"batch": B, "ms_per_step": ms, "tokens_per_s": B / (ms / 1e3), "kernels": nk, "experts_hit_per_layer": hit / model.L,
                      "weight_GBps": (dense + hit * expert_bytes) / ms / 1e6})
     ctx.check_device_error()

@@ -47,16 +47,24 @@ def test_stacked_gate_up_weight_layout(ctx):
         w.free()
 
 
-@pytest.mark.parametrize("fused", [True, False])
+def _form(layer, form):
+    """stream: the small-rows streaming kernel whatever the row count; fused: the tcgen05 grouped product with the SwiGLU
+    epilogue; three: gate, up and down as three tcgen05 products."""
+    layer.SMALL_ROWS = {"stream": 1 << 20, "fused": 0, "three": 0}[form]
+    assert (layer.w_gate_up is not None) == (form != "three")
+
+
+@pytest.mark.parametrize("form", ["stream", "fused", "three"])
 @pytest.mark.parametrize("T", [1, 7, 64, 300])
-def test_moe_ffn_against_oracle(ctx, T, fused):
+def test_moe_ffn_against_oracle(ctx, T, form):
+    fused = form != "three"
     H, I, E, k = 256, 384, 8, 2
     wg, wu, wd = (Mxfp4Weight.generate(ctx, 4, 910 + i, E, n, kk) for i, (n, kk) in enumerate(((I, H), (I, H), (H, I))))
     router = round_to_dtype(gen_normal(4, 920, E * H, 0.02).reshape(E, H), BF16)
     bias = (-1.1 * np.log(np.arange(1, E + 1))).astype(np.float32) * 0.05      # mild Zipf skew
     x = round_to_dtype(gen_normal(4, 921, T * H).reshape(T, H), BF16)
     layer = MoeFfn(ctx, H, I, E, k, ctx.to_device(router, BF16), ctx.to_device(bias), wg, wu, wd, fused_swiglu=fused)
-    assert (layer.w_gate_up is not None) == fused
+    _form(layer, form)
     keep = {}
     out = ctx.to_host(layer.forward(ctx.to_device(x, BF16), T, out_dtype=F32, keep=keep), F32, T * H).reshape(T, H)
     ctx.check_device_error()
@@ -78,9 +86,9 @@ def test_moe_ffn_against_oracle(ctx, T, fused):
         w.free()
 
 
-@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("form", ["stream", "fused", "three"])
 @pytest.mark.parametrize("T", [1, 64])
-def test_moe_ffn_at_the_full_layer_size(ctx, T, fused):
+def test_moe_ffn_at_the_full_layer_size(ctx, T, form):
     """The MoE configuration's own dimensions (hidden = expert intermediate = 2880, 32 experts, top-4, Zipf-skewed router
     bias): routing and permutation exact, values at the contract tolerance.  The oracle dequantises only the experts that
     are hit, from the bytes the device holds; the device generator is checked against the oracle's on expert 0."""
@@ -92,7 +100,9 @@ def test_moe_ffn_at_the_full_layer_size(ctx, T, fused):
     router = round_to_dtype(gen_normal(4, 950, E * H, 0.02).reshape(E, H), BF16)
     bias = (-1.1 * np.log(np.arange(1, E + 1))).astype(np.float32)              # expert load roughly Zipf(1.1)
     x = round_to_dtype(gen_normal(4, 951, T * H).reshape(T, H), BF16)
+    fused = form != "three"
     layer = MoeFfn(ctx, H, I, E, k, ctx.to_device(router, BF16), ctx.to_device(bias), *ws, fused_swiglu=fused)
+    _form(layer, form)
     keep = {}
     out = ctx.to_host(layer.forward(ctx.to_device(x, BF16), T, out_dtype=F32, keep=keep), F32, T * H).reshape(T, H)
     ctx.check_device_error()
