@@ -117,7 +117,7 @@ class MoeDecoder:
         return tok
 
     # ---- one decode step of B sequences: the launches of a step, replayed from a CUDA graph per batch size
-    def _enqueue_step(self, B):
+    def _enqueue_step(self, B, splits):
         ctx, lib, c, b = self.ctx, self.ctx.lib, self.cfg, self._rows(B)
         ctx._check(lib.blum_gather(ctx.h, self.embed.ptr, F32, self.V, self.H, b["ids"].ptr, B, b["x"].ptr, BF16))
         f = None
@@ -126,7 +126,7 @@ class MoeDecoder:
                                         b["x"].ptr if f is not None else None, BF16, B, self.H))
             self._mm(w["wqkv"], self.qkv_rows, self.H, b["xn"], b["qkv"], B)
             ctx._check(lib.blum_rope_attn_decode_paged(ctx.h, self.kv.h, l, b["qkv"].ptr, BF16, self.nq, c["rope_theta"], b["seq"].ptr,
-                                                       b["ctxl"].ptr, B, self.max_splits, b["scratch"].ptr, b["attn"].ptr))
+                                                       b["ctxl"].ptr, B, splits, b["scratch"].ptr, b["attn"].ptr))
             self._mm(w["wo"], self.H, self.nq * self.d, b["attn"], b["o"], B)
             ctx._check(lib.blum_rmsnorm(ctx.h, b["x"].ptr, b["o"].ptr, w["ffn_norm"].ptr, c["rms_eps"], b["xn"].ptr, b["x"].ptr, BF16, B, self.H))
             f = w["ffn"].enqueue(b["xn"])
@@ -144,19 +144,26 @@ class MoeDecoder:
         self._upload(b["ids"], toks)
         self._upload(b["seq"], seqs)
         self._upload(b["ctxl"], [n + 1 for n in lens])
-        if B not in self._graphs:
-            for w in self.layers:
-                w["ffn"].plan(B)
+        # context splits of the attention kernel: one per 256 cached positions of the longest sequence, a power of two
+        splits = 1
+        while splits < self.max_splits and splits * 256 < max(lens) + 1:
+            splits *= 2
+        key = (B, splits)
+        if key not in self._graphs:
+            if not any(k[0] == B for k in self._graphs):
+                for w in self.layers:
+                    w["ffn"].plan(B)
             # (every layer's planned buffers are its own, so the captured step names them all)
-            self._enqueue_step(B)                          # plain pass (sizes workspaces outside the capture); the captured step
+            self._enqueue_step(B, splits)                  # plain pass (sizes workspaces outside the capture); the captured step
                                                            # below repeats it on the same positions with the same values
             ctx.sync()
             ctx._check(lib.blum_graph_begin(ctx.h))
-            self._enqueue_step(B)
+            self._enqueue_step(B, splits)
             g, nk = C.c_void_p(), C.c_int()
             ctx._check(lib.blum_graph_end(ctx.h, C.byref(g), C.byref(nk)))
-            self._graphs[B] = (g, nk.value)
-        g, nk = self._graphs[B]
+            self._graphs[key] = (g, nk.value)
+        self._last_key = key
+        g, nk = self._graphs[key]
         ctx._check(lib.blum_graph_launch(ctx.h, g, nk))
         out = b["next"].download(np.int32, B)
         ctx.check_device_error()
@@ -165,8 +172,9 @@ class MoeDecoder:
         return out
 
     def step_graph(self, B):
-        """(graph handle, kernel count) of the captured B-row step, for timing loops."""
-        return self._graphs[B]
+        """(graph handle, kernel count) of the B-row step captured last, for timing loops."""
+        assert self._last_key[0] == B
+        return self._graphs[self._last_key]
 
     @property
     def weight_bytes(self):

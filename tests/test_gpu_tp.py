@@ -126,7 +126,8 @@ def _ep_rank_main(rank, size, id_path, out_q):
         router = ctx.to_device(round_to_dtype(gen_normal(4, 920, E * H, 0.02).reshape(E, H), BF16), BF16)
         bias = ctx.to_device((-0.05 * 1.1 * np.log(np.arange(1, E + 1))).astype(np.float32))
         x = ctx.to_device(round_to_dtype(gen_normal(4, 930 + rank, T * H).reshape(T, H), BF16), BF16)
-        want = ctx.to_host(MoeFfn(ctx, H, I, E, k, router, bias, *full).forward(x, T, out_dtype=F32), F32, T * H)
+        # the sharded layer multiplies gate, up and down as three tensor-core products: bit identity is against that form
+        want = ctx.to_host(MoeFfn(ctx, H, I, E, k, router, bias, *full, fused_swiglu=False).forward(x, T, out_dtype=F32), F32, T * H)
         ep = ExpertParallelMoe(ctx, comm, H, I, E, k, router, bias, *mine)
         got = ctx.to_host(ep.forward(x, T, out_dtype=F32), F32, T * H)
         got2 = ctx.to_host(ep.forward(x, T, out_dtype=F32), F32, T * H)
