@@ -127,16 +127,19 @@ enum { WF_Q8_0 = 0, WF_MXFP4 = 1, WF_BF16 = 2 };
 // KH: 64-wide k halves per pipeline stage.  One stage is one hand-over (barrier wait, MMA issue, commit) whatever it holds, and
 // at small token tiles that fixed cost, not the tensor work, sets the pace: two halves per stage halve the hand-overs.
 // CPS: CTAs meant to share an SM (the ring gets 1/CPS of the shared memory)
-template <int TN, int WF, int KH = 1, int CPS = 1> struct GtCfg {
+// NA: token tiles (accumulators) per CTA.  Every dequantised weight tile is multiplied against NA token tiles of TN rows, each
+// with its own TMEM columns: the conversion work per flop, which is what bounds the kernel at large M, divides by NA.
+template <int TN, int WF, int KH = 1, int CPS = 1, int NA = 1> struct GtCfg {
     static constexpr int A_BYTES = GT_BN * GT_BK * 2;       // 16384, bf16 weights in UMMA layout
-    static constexpr int X_BYTES = TN * GT_BK * 2;          // bf16 activations
+    static constexpr int X_TILE_BYTES = TN * GT_BK * 2;     // bf16 activations of one token tile
+    static constexpr int X_BYTES = NA * X_TILE_BYTES;
     // raw weight staging per stage: int8 [128][64], packed e2m1 nibbles [128][32], or none (bf16 lands in A directly)
     static constexpr int Q_BYTES = WF == WF_Q8_0 ? GT_BN * GT_BK : WF == WF_MXFP4 ? GT_BN * GT_BK / 2 : 0;
     static constexpr int HALF_BYTES = A_BYTES + X_BYTES + Q_BYTES;
     static constexpr int STAGE_BYTES = KH * HALF_BYTES;
     static constexpr int STAGES = (200 * 1024 / CPS) / STAGE_BYTES > 8 ? 8 : (200 * 1024 / CPS) / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;   // + alignment slack
-    static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
+    static constexpr int TMEM_COLS = NA * TN < 32 ? 32 : NA * TN;
     static constexpr int TX_BYTES = KH * ((WF == WF_BF16 ? A_BYTES : Q_BYTES) + X_BYTES);
 };
 
@@ -147,10 +150,12 @@ __device__ __forceinline__ float e2m1_value(int code) {
     return (code & 8) ? -mag : mag;
 }
 
-template <int TN, typename TY, int WF, int KH, int CPS>
+template <int TN, typename TY, int WF, int KH, int CPS, int NA>
 __global__ void __launch_bounds__(GT_THREADS, CPS)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, const GemmTcParams p) {
-    using C = GtCfg<TN, WF, KH, CPS>;
+    using C = GtCfg<TN, WF, KH, CPS, NA>;
+    constexpr int TT = NA * TN;                                  // tokens of a CTA: NA tiles of TN consecutive rows
+    static_assert(C::TMEM_COLS <= 512 && (C::TMEM_COLS & (C::TMEM_COLS - 1)) == 0, "tensor memory columns: a power of two up to 512");
     static_assert(C::STAGES >= 2 && CPS * C::TMEM_COLS <= 512, "ring or tensor memory does not fit this many CTAs per SM");
     static_assert(KH == 1 || WF == WF_Q8_0, "two halves per stage are built for Q8_0 weights only");
     extern __shared__ unsigned char smem_raw[];
@@ -172,14 +177,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             g = p.tile_list[1 + 2 * blockIdx.y];
             m0 = p.tile_list[2 + 2 * blockIdx.y];
         } else {
-            m0 = p.group_offsets[g] + blockIdx.y * TN;
+            m0 = p.group_offsets[g] + blockIdx.y * TT;
         }
         m_end = p.group_offsets[g + 1];
         if (m0 >= m_end) return;                               // whole CTA: nothing allocated yet
         wrow0 = g * p.N;
         ks0 = 0; nk = p.ksteps_total;
     } else {
-        m0 = blockIdx.y * TN; m_end = p.M; wrow0 = 0;
+        m0 = blockIdx.y * TT; m_end = p.M; wrow0 = 0;
         ks0 = blockIdx.z * p.ksteps_per_split;
         nk = min(p.ksteps_total, ks0 + p.ksteps_per_split) - ks0;
     }
@@ -229,7 +234,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     if (WF == WF_Q8_0) tma_load_2d(q_s(s, h), &wmap, k, wrow0 + n0, &full[s]);
                     else if (WF == WF_MXFP4) tma_load_2d(q_s(s, h), &wmap, k / 2, wrow0 + n0, &full[s]);     // two weights per byte
                     else tma_load_2d(a_s(s, h), &wmap, k, wrow0 + n0, &full[s]);                              // bf16, 128-byte swizzle
-                    tma_load_2d(x_s(s, h), &xmap, k, m0, &full[s]);
+#pragma unroll
+                    for (int a = 0; a < NA; a++)        // rows past the end of x arrive as zeros
+                        tma_load_2d(x_s(s, h) + a * C::X_TILE_BYTES, &xmap, k, m0 + a * TN, &full[s]);
                 }
                 tma_issued = it + 1;
             }
@@ -247,10 +254,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
                 for (int h = 0; h < KH; h++) {
                     const uint64_t adesc = umma_desc_sw128(smem_u32(a_s(s, h)));
-                    const uint64_t bdesc = umma_desc_sw128(smem_u32(x_s(s, h)));
 #pragma unroll
-                    for (int kk = 0; kk < GT_BK / 16; kk++)   // 16 bf16 = 32 bytes = 2 descriptor units along K
-                        umma_bf16(tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (it > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                    for (int a = 0; a < NA; a++) {
+                        const uint64_t bdesc = umma_desc_sw128(smem_u32(x_s(s, h) + a * C::X_TILE_BYTES));
+#pragma unroll
+                        for (int kk = 0; kk < GT_BK / 16; kk++)   // 16 bf16 = 32 bytes = 2 descriptor units along K
+                            umma_bf16(tmem + (uint32_t)(a * TN), adesc + 2 * kk, bdesc + 2 * kk, idesc, (it > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                    }
                 }
                 umma_commit(&empty[s]);
             }
@@ -356,10 +366,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31 belong to this warp
             const int n = n0 + quarter * 32 + lane;
             constexpr int WPQ = GT_CONV_WARPS / 4;                  // warps per TMEM lane quarter: they split the columns
-            constexpr int COLS_PER = (TN / WPQ < 32) ? 32 : TN / WPQ;
+            constexpr int COLS_PER = (TT / WPQ < 32) ? 32 : TT / WPQ;
             const int cbeg = ((warp - 2) >> 2) * COLS_PER;
 #pragma unroll 1
-            for (int c0 = cbeg; c0 < cbeg + COLS_PER && c0 < TN; c0 += 32) {
+            for (int c0 = cbeg; c0 < cbeg + COLS_PER && c0 < TT; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -480,11 +490,11 @@ __global__ void f32_to_out_kernel(const float* __restrict__ src, void* __restric
     }
 }
 
-template <int TN, typename TY, int WF, int KH = 1, int CPS = 1>
+template <int TN, typename TY, int WF, int KH = 1, int CPS = 1, int NA = 1>
 static int launch_tc(blum_ctx* ctx, const CUtensorMap& wmap, const CUtensorMap& xmap, const GemmTcParams& p, dim3 grid) {
-    auto kern = tc_gemm_kernel<TN, TY, WF, KH, CPS>;
-    BLUM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GtCfg<TN, WF, KH, CPS>::SMEM));
-    kern<<<grid, GT_THREADS, GtCfg<TN, WF, KH, CPS>::SMEM, ctx->stream>>>(wmap, xmap, p);
+    auto kern = tc_gemm_kernel<TN, TY, WF, KH, CPS, NA>;
+    BLUM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GtCfg<TN, WF, KH, CPS, NA>::SMEM));
+    kern<<<grid, GT_THREADS, GtCfg<TN, WF, KH, CPS, NA>::SMEM, ctx->stream>>>(wmap, xmap, p);
     BLUM_LAUNCH_CHECK(ctx);
     return BLUM_OK;
 }
@@ -499,6 +509,8 @@ static int launch_tc_pair(blum_ctx* ctx, int TN, bool f32_store, const CUtensorM
     return TN == 32 ? TC2(32) : TC2(64);
 #undef TC2
 }
+
+static int g_group_tn = 0;     // experiment: token tile of grouped products (0: from the rows-per-group hint)
 
 template <int WF>
 static int launch_tc_tn(blum_ctx* ctx, int TN, bool f32_store, const CUtensorMap& wmap, const CUtensorMap& xmap, const GemmTcParams& p, dim3 grid) {
@@ -522,8 +534,14 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     BLUM_REQUIRE(ctx, ((uintptr_t)x % 16) == 0 && ((uintptr_t)wdata % 16) == 0, "tc gemm: operands must be 16-byte aligned");
     BLUM_REQUIRE(ctx, encode_tiled_fn() != nullptr, "tc gemm: tensor maps are not available from this driver");
     const int64_t mt = groups > 0 ? (rows_per_group_hint > 0 ? rows_per_group_hint : M) : M;
-    const int TN = mt <= 32 ? 32 : mt <= 64 ? 64 : mt <= 128 ? 128 : 256;
-    const int n_tiles = (N + GT_BN - 1) / GT_BN, m_tiles = (int)((M + TN - 1) / TN);
+    int TN = mt <= 32 ? 32 : mt <= 64 ? 64 : mt <= 128 ? 128 : 256;
+    if (groups > 0 && g_group_tn > 0 && mt > 32) TN = g_group_tn;
+    const int n_tiles = (N + GT_BN - 1) / GT_BN;
+    // dense products of 512 rows and more: two 256-row token tiles per CTA (one dequantised weight tile feeds both), as long
+    // as the grid still covers most of the SMs
+    const bool two_acc = groups == 0 && wf != WF_MXFP4 && TN == 256 && M >= 512 && (int64_t)n_tiles * ((M + 511) / 512) * 4 >= (int64_t)ctx->sm_count * 3;
+    const int TT = two_acc ? 512 : TN;
+    const int m_tiles = (int)((M + TT - 1) / TT);
     // small token tiles of the dense Q8_0 product take two 64-wide halves per stage (half as many hand-overs)
     const bool pair = wf == WF_MXFP4 && groups > 0 && TN <= 64;
     const int KH = (!pair && wf == WF_Q8_0 && groups == 0 && TN <= 64 && K % (2 * GT_BK) == 0) ? 2 : 1;
@@ -584,6 +602,9 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     if (KH == 2) {
         rc = TN == 32 ? (f32_store ? launch_tc<32, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<32, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid))
                       : (f32_store ? launch_tc<64, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<64, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid));
+    } else if (two_acc) {
+        rc = wf == WF_Q8_0 ? (f32_store ? launch_tc<256, float, WF_Q8_0, 1, 1, 2>(ctx, wmap, xmap, p, grid) : launch_tc<256, __nv_bfloat16, WF_Q8_0, 1, 1, 2>(ctx, wmap, xmap, p, grid))
+                           : (f32_store ? launch_tc<256, float, WF_BF16, 1, 1, 2>(ctx, wmap, xmap, p, grid) : launch_tc<256, __nv_bfloat16, WF_BF16, 1, 1, 2>(ctx, wmap, xmap, p, grid));
     } else if (pair)
         rc = launch_tc_pair<WF_MXFP4>(ctx, TN, f32_store, wmap, xmap, p, grid);
     else
@@ -603,6 +624,8 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
 // decode step, anything recorded between blum_graph_begin/end) keep its address.  An outgrown buffer moves to the context's
 // retired list and is released by blum_ctx_destroy.  Growth is refused while the stream is capturing, because cudaMalloc
 // would invalidate the capture.
+int blum_tc_gemm_set_group_tn(int tn) { g_group_tn = tn; return BLUM_OK; }
+
 int blum_gemm_ws_reserve(blum_ctx* ctx, size_t bytes) {
     if (ctx->gemm_ws_bytes >= bytes) return BLUM_OK;
     cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;

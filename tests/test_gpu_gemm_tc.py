@@ -44,7 +44,7 @@ def test_tc_gemm_model_shapes(ctx, orc, n, k, m):
 
 @pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096), (8192, 28672)])
 def test_operator_sweep_sizes_on_a_sub_block(ctx, k, n):
-    """Every (K, N) of the operator sweep at M in {8, 64, 512, 4096}, bf16 in and out: several token tiles at full N,
+    """Every (K, N) of the operator sweep at M in {8, 64, 512, 4096} (and two ragged row counts), bf16 in and out: several token tiles at full N,
     split-K at full size and the ragged last tiles.  The full products are too slow for the CPU oracle, so a sub-block is
     checked instead: up to 64 rows of x (first, last and scattered) times 256 output columns (the first and the last
     128-row weight tile plus scattered ones), computed in float64 from the host generator's quants and scales."""
@@ -55,7 +55,8 @@ def test_operator_sweep_sizes_on_a_sub_block(ctx, k, n):
     cols = np.unique(np.concatenate([np.arange(0, 64), np.arange(n - 64, n), rng.integers(64, n - 64, 128)]))
     wsub = q[cols].astype(np.float64) * np.repeat(d[cols].view(np.float16).astype(np.float64), 32, axis=1)
     mm = QuantizedMatmul(ctx, BF16, BF16)
-    for m in (8, 64, 512, 4096):
+    # 700 and 1300 rows: CTAs that hold two 256-row token tiles meet a ragged and a wholly empty second tile
+    for m in (8, 64, 512, 4096) + ((700, 1300) if n == 14336 else ()):
         x = round_to_dtype(gen_normal(1, tid + m, m * k).reshape(m, k), BF16)
         rows = np.unique(np.concatenate([np.arange(0, min(m, 8)), np.arange(max(m - 8, 0), m), rng.integers(0, m, 48)]))
         got = ctx.to_host(mm.process(ctx.to_device(x, BF16), w, m), BF16, m * n).reshape(m, n)[np.ix_(rows, cols)]
