@@ -79,9 +79,6 @@ int64_t blum_launch_count(blum_ctx* ctx);
  * `copies` packed copies are cycled so that every launch streams from HBM; `iters` launches in one CUDA graph. */
 int blum_rows_matmul_timed(blum_ctx* ctx, const blum_q8_weight* w, int M, blum_dtype x_dtype, int copies, int iters, float* avg_us);
 
-/* Experiment switch: token tile of grouped tcgen05 products with more than 32 rows per group (0: chosen from the hint). */
-int blum_tc_gemm_set_group_tn(int tn);
-
 #ifdef __cplusplus
 }
 #endif

@@ -94,6 +94,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+// the same box towards L2 only
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
 // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart (the canonical layout TMA SWIZZLE_128B produces)
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     uint64_t desc = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
@@ -137,9 +141,10 @@ template <int TN, int WF, int KH = 1, int CPS = 1, int NA = 1> struct GtCfg {
     static constexpr int Q_BYTES = WF == WF_Q8_0 ? GT_BN * GT_BK : WF == WF_MXFP4 ? GT_BN * GT_BK / 2 : 0;
     static constexpr int HALF_BYTES = A_BYTES + X_BYTES + Q_BYTES;
     static constexpr int STAGE_BYTES = KH * HALF_BYTES;
-    static constexpr int STAGES = (200 * 1024 / CPS) / STAGE_BYTES > 8 ? 8 : (200 * 1024 / CPS) / STAGE_BYTES;
+    static constexpr int RING_BYTES = (NA > 1 ? 218 : 200) * 1024 / CPS;   // two token tiles: three stages of 72 KB just fit
+    static constexpr int STAGES = RING_BYTES / STAGE_BYTES > 8 ? 8 : RING_BYTES / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;   // + alignment slack
-    static constexpr int TMEM_COLS = NA * TN < 32 ? 32 : NA * TN;
+    static constexpr int TMEM_COLS = NA * TN <= 32 ? 32 : NA * TN <= 64 ? 64 : NA * TN <= 128 ? 128 : NA * TN <= 256 ? 256 : 512;
     static constexpr int TX_BYTES = KH * ((WF == WF_BF16 ? A_BYTES : Q_BYTES) + X_BYTES);
 };
 
@@ -226,6 +231,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             asm volatile("prefetch.tensormap [%0];" ::"l"(&xmap) : "memory");
             for (int it = 0; it < nk; it++) {
                 const int s = it % C::STAGES;
+                if (NA > 1 && it + 3 < nk) {
+                    // Two token tiles leave room for two stages only, so a stage's copy is requested just one MMA ahead and its
+                    // latency would be in the loop: the weight box of three steps on is pulled into L2 now (x is shared by
+                    // all CTAs of a token tile and is there already).
+                    const int kp = (ks0 + it + 3) * KH * GT_BK;
+                    tma_prefetch_2d(&wmap, WF == WF_MXFP4 ? kp / 2 : kp, wrow0 + n0);
+                }
                 if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) - 1) & 1, abortp)) break;
                 mbar_expect_tx(&full[s], C::TX_BYTES);
 #pragma unroll
@@ -510,8 +522,6 @@ static int launch_tc_pair(blum_ctx* ctx, int TN, bool f32_store, const CUtensorM
 #undef TC2
 }
 
-static int g_group_tn = 0;     // experiment: token tile of grouped products (0: from the rows-per-group hint)
-
 template <int WF>
 static int launch_tc_tn(blum_ctx* ctx, int TN, bool f32_store, const CUtensorMap& wmap, const CUtensorMap& xmap, const GemmTcParams& p, dim3 grid) {
 #define TC(tn) (f32_store ? launch_tc<tn, float, WF>(ctx, wmap, xmap, p, grid) : launch_tc<tn, __nv_bfloat16, WF>(ctx, wmap, xmap, p, grid))
@@ -535,12 +545,30 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
     BLUM_REQUIRE(ctx, encode_tiled_fn() != nullptr, "tc gemm: tensor maps are not available from this driver");
     const int64_t mt = groups > 0 ? (rows_per_group_hint > 0 ? rows_per_group_hint : M) : M;
     int TN = mt <= 32 ? 32 : mt <= 64 ? 64 : mt <= 128 ? 128 : 256;
-    if (groups > 0 && g_group_tn > 0 && mt > 32) TN = g_group_tn;
+    // grouped products are bound by the conversion of the weight tiles, which a wider token tile spreads over more rows:
+    // skewed expert loads put most rows into a few experts (MoE layer at 1024 tokens: 986 us with 128-row tiles, 911 us with 256)
+    if (groups > 0 && TN == 128) TN = 256;
     const int n_tiles = (N + GT_BN - 1) / GT_BN;
-    // dense products of 512 rows and more: two 256-row token tiles per CTA (one dequantised weight tile feeds both), as long
-    // as the grid still covers most of the SMs
-    const bool two_acc = groups == 0 && wf != WF_MXFP4 && TN == 256 && M >= 512 && (int64_t)n_tiles * ((M + 511) / 512) * 4 >= (int64_t)ctx->sm_count * 3;
-    const int TT = two_acc ? 512 : TN;
+    // Dense products with more than one wave of 256-row tiles: a CTA can hold TWO token tiles (one dequantised weight tile
+    // feeds both, so the conversion work per flop halves): 2 x 192 rows with three pipeline stages, or 2 x 256 rows with
+    // two.  Which one pays depends on how the tiles fill whole waves of the grid; time per k-step of a CTA, measured:
+    // 0.73 us for 256 rows, 0.79 us for 2 x 192, 1.23 us for 2 x 256.
+    int NA = 1;
+    if (groups == 0 && wf != WF_MXFP4 && TN == 256 && (int64_t)n_tiles * ((M + 255) / 256) >= ctx->sm_count) {
+        const int tt[3] = {256, 384, 512};
+        const double step_us[3] = {0.73, 0.79, 1.23};
+        double best = 1e30;
+        int pick = 0;
+        for (int o = 0; o < 3; o++) {
+            const int64_t ctas = (int64_t)n_tiles * ((M + tt[o] - 1) / tt[o]);
+            const double cost = (double)((ctas + ctx->sm_count - 1) / ctx->sm_count) * step_us[o];
+            if (cost < best) { best = cost; pick = o; }
+        }
+        if (pick == 1) { TN = 192; NA = 2; }
+        else if (pick == 2) NA = 2;
+    }
+    const bool two_acc = NA == 2;
+    const int TT = NA * TN;
     const int m_tiles = (int)((M + TT - 1) / TT);
     // small token tiles of the dense Q8_0 product take two 64-wide halves per stage (half as many hand-overs)
     const bool pair = wf == WF_MXFP4 && groups > 0 && TN <= 64;
@@ -603,8 +631,9 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
         rc = TN == 32 ? (f32_store ? launch_tc<32, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<32, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid))
                       : (f32_store ? launch_tc<64, float, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid) : launch_tc<64, __nv_bfloat16, WF_Q8_0, 2>(ctx, wmap, xmap, p, grid));
     } else if (two_acc) {
-        rc = wf == WF_Q8_0 ? (f32_store ? launch_tc<256, float, WF_Q8_0, 1, 1, 2>(ctx, wmap, xmap, p, grid) : launch_tc<256, __nv_bfloat16, WF_Q8_0, 1, 1, 2>(ctx, wmap, xmap, p, grid))
-                           : (f32_store ? launch_tc<256, float, WF_BF16, 1, 1, 2>(ctx, wmap, xmap, p, grid) : launch_tc<256, __nv_bfloat16, WF_BF16, 1, 1, 2>(ctx, wmap, xmap, p, grid));
+#define TC_NA2(tn, W) (f32_store ? launch_tc<tn, float, W, 1, 1, 2>(ctx, wmap, xmap, p, grid) : launch_tc<tn, __nv_bfloat16, W, 1, 1, 2>(ctx, wmap, xmap, p, grid))
+        rc = wf == WF_Q8_0 ? (TN == 192 ? TC_NA2(192, WF_Q8_0) : TC_NA2(256, WF_Q8_0)) : (TN == 192 ? TC_NA2(192, WF_BF16) : TC_NA2(256, WF_BF16));
+#undef TC_NA2
     } else if (pair)
         rc = launch_tc_pair<WF_MXFP4>(ctx, TN, f32_store, wmap, xmap, p, grid);
     else
@@ -624,8 +653,6 @@ int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, i
 // decode step, anything recorded between blum_graph_begin/end) keep its address.  An outgrown buffer moves to the context's
 // retired list and is released by blum_ctx_destroy.  Growth is refused while the stream is capturing, because cudaMalloc
 // would invalidate the capture.
-int blum_tc_gemm_set_group_tn(int tn) { g_group_tn = tn; return BLUM_OK; }
-
 int blum_gemm_ws_reserve(blum_ctx* ctx, size_t bytes) {
     if (ctx->gemm_ws_bytes >= bytes) return BLUM_OK;
     cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
