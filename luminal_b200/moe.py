@@ -113,10 +113,16 @@ class MoeFfn:
         return sorted_src, slot_of, offsets
 
     def plan(self, T, out_dtype=BF16):
-        """Pre-allocates every intermediate of a T-token step (so that `enqueue` allocates nothing and can be captured)."""
+        """Pre-allocates every intermediate of a T-token step (so that `enqueue` allocates nothing and can be captured).
+        Plans are kept per (T, out_dtype): planning the same shape again only makes it the current one."""
         ctx, n = self.ctx, T * self.k
+        if not hasattr(self, "_plans"):
+            self._plans = {}
+        if (T, out_dtype) in self._plans:
+            self._plan = self._plans[(T, out_dtype)]
+            return self._plan
         a = lambda nbytes: ctx.alloc(max(nbytes, 16))
-        self._plan = dict(T=T, out_dtype=out_dtype, ids=a(n * 4), gates=a(n * 4), sorted_src=a(n * 4), slot_of=a(n * 4),
+        self._plan = self._plans[(T, out_dtype)] = dict(T=T, out_dtype=out_dtype, ids=a(n * 4), gates=a(n * 4), sorted_src=a(n * 4), slot_of=a(n * 4),
                           offsets=a((self.E + 1) * 4), xp=a(n * self.H * 2),
                           g=a(n * self.I * 2) if self.w_gate_up is None else None, u=a(n * self.I * 2) if self.w_gate_up is None else None,
                           mid=a(n * self.I * 2), yp=a(n * self.H * 2), out=a(T * self.H * (4 if out_dtype == F32 else 2)))

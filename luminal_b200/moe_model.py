@@ -75,7 +75,7 @@ class MoeDecoder:
         self._mm(self.head, self.V, self.H, b["xn"], b["logits"], rows, F32)
         ctx._check(lib.blum_argmax(ctx.h, b["logits"].ptr, F32, rows, self.V, b["next"].ptr))
 
-    # ---- prompt pass of one sequence (eager; every operator allocates nothing but the feed-forward's intermediates)
+    # ---- prompt pass of one sequence (eager launches; buffers are kept per prompt length)
     def prefill(self, seq, ids, want_logits=False):
         ctx, lib, c = self.ctx, self.ctx.lib, self.cfg
         T, p0 = len(ids), self.kv.seq_len(seq)
@@ -99,8 +99,8 @@ class MoeDecoder:
             ctx._check(lib.blum_attn_prefill_paged(ctx.h, self.kv.h, l, b["q"].ptr, BF16, self.nq, seq, p0, T, b["attn"].ptr))
             self._mm(w["wo"], self.H, self.nq * self.d, b["attn"], b["o"], T)
             ctx._check(lib.blum_rmsnorm(ctx.h, b["x"].ptr, b["o"].ptr, w["ffn_norm"].ptr, c["rms_eps"], b["xn"].ptr, b["x"].ptr, BF16, T, self.H))
-            keep = {} if self.trace is not None else None
-            f = w["ffn"].forward(b["xn"], T, keep=keep)
+            keep = w["ffn"].plan(T)                                 # cached per prompt length: no allocation after the first prompt
+            f = w["ffn"].enqueue(b["xn"])
             if self.trace is not None:
                 x_mid = ctx.to_host(b["x"], BF16, T * self.H)
                 ids_l = keep["ids"].download(np.int32, T * self.k)
@@ -150,9 +150,8 @@ class MoeDecoder:
             splits *= 2
         key = (B, splits)
         if key not in self._graphs:
-            if not any(k[0] == B for k in self._graphs):
-                for w in self.layers:
-                    w["ffn"].plan(B)
+            for w in self.layers:
+                w["ffn"].plan(B)                               # (kept per batch size: makes it the layer's current plan)
             # (every layer's planned buffers are its own, so the captured step names them all)
             self._enqueue_step(B, splits)                  # plain pass (sizes workspaces outside the capture); the captured step
                                                            # below repeats it on the same positions with the same values
