@@ -25,6 +25,32 @@ Q8_CASES = [(64, 256, 1), (96, 512, 3), (40, 1024, 8)]   # (N, K, M); tensor id 
 SAMPLE_CASES = [(1.0, 1.0, 1), (0.7, 0.9, 2), (2.0, 0.5, 3), (1.0, 0.02, 4)]
 
 
+# MXFP4 mixture-of-experts layer (seed 4): hidden 64, intermediate 96, 4 experts, top-2, 9 tokens; expert weights from tensor
+# ids 810-812, router id 820, tokens id 821; both forms of the gate/up products (rounded to bf16 before the SwiGLU or not)
+MOE_CASE = dict(H=64, I=96, E=4, k=2, T=9)
+
+
+def moe_inputs(orc):
+    from oracle import moe as omoe
+    c = MOE_CASE
+    ws = [omoe.dequant_mxfp4(*omoe.gen_mxfp4(4, 810 + i, c["E"], n, kk)) for i, (n, kk) in enumerate(((c["I"], c["H"]), (c["I"], c["H"]), (c["H"], c["I"])))]
+    router = omoe.round_bf16(orc.gen_normal(4, 820, c["E"] * c["H"], 0.02).reshape(c["E"], c["H"]))
+    bias = (-0.3 * np.log(np.arange(1, c["E"] + 1))).astype(np.float32)
+    x = omoe.round_bf16(orc.gen_normal(4, 821, c["T"] * c["H"]).reshape(c["T"], c["H"]))
+    return x, router, bias, ws
+
+
+def compute_moe(orc):
+    from oracle import moe as omoe
+    x, router, bias, ws = moe_inputs(orc)
+    out = {}
+    for key, rnd in (("moe_out", True), ("moe_out_f32_gate_up", False)):
+        y, ids, gates = omoe.moe_ffn(x, router, bias, ws[0], ws[1], ws[2], MOE_CASE["k"], round_gate_up=rnd)
+        out[key] = y
+    out["moe_ids"], out["moe_gates"] = ids, gates
+    return out
+
+
 def compute(orc):
     out = {}
     for i, (n, k, m) in enumerate(Q8_CASES):
@@ -67,6 +93,7 @@ def compute(orc):
         ids, gaps = model.greedy(orc.gen_token_ids(0, 1, 6, TP_CFG["vocab"]), 8)
         out[key] = np.array(ids, np.int32)
         out[key.replace("ids", "gaps")] = np.array(gaps, np.float32)
+    out.update(compute_moe(orc))
     logits = orc.gen_normal(5, 700, 8 * 1000, 3.0).reshape(8, 1000)
     out["sample_ids"] = np.array([[orc.sample_top_p(logits[r], t, p, sd, r % 3, 10 * r + c) for r in range(8)]
                                   for c, (t, p, sd) in enumerate(SAMPLE_CASES)], np.int32)
