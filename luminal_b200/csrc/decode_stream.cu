@@ -126,9 +126,11 @@ __device__ __forceinline__ float ds_wait_value(const unsigned long long* ptr, ui
 __device__ __forceinline__ void ds_sync() { __syncthreads(); }
 __device__ __forceinline__ int ds_sync_and(int pred) { return __syncthreads_and(pred); }
 
+static_assert(DS_PARTIAL_SLOTS * 16 >= DS_WARPS * 128, "the attention phase borrows the partial-sum slots as [DS_WARPS][128]");
 struct DsShared {
     uint64_t full[DS_STAGES];
-    float partial[DS_PARTIAL_SLOTS][16];            // per-unit row sums waiting for the rest of their group
+    float partial[DS_PARTIAL_SLOTS][16];            // per-unit row sums waiting for the rest of their group (the attention phase
+                                                    // borrows it as [DS_WARPS][128])
     int gcnt[DS_PARTIAL_SLOTS];                     // units of a group deposited so far (indexed by group % slots)
     int pbusy[DS_PARTIAL_SLOTS];                    // 1 while a slot of `partial` holds sums that have not been added up yet
     int xstate[DS_MAX_SLICES];                      // 4 * phase + {1: being staged, 2: staged} per 512-element slice of x
@@ -137,8 +139,7 @@ struct DsShared {
     float rsn[64], rcs[64];                         // rotation of the step's position
     float sc[DS_ATTN_TILE];
     long long koff[DS_ATTN_TILE];
-    float o_part[DS_ATTN_PARTS][128];
-    float l_part[DS_ATTN_PARTS];
+    float l_part[DS_WARPS];                         // every warp's share of the softmax denominator (its share of P V lives in `partial`)
     unsigned long long seq;
     int abort;
     float resid[DS_RESIDUAL_ROWS];                  // residual rows of the groups this CTA finishes (o_proj / down)
@@ -387,19 +388,23 @@ __device__ __forceinline__ void ds_attention(const DsParams& p, int layer, int p
             }
         }
         const float4 q4 = *reinterpret_cast<const float4*>(&sh.q[lane * 4]);
-        float m_run = -INFINITY, l_run = 0.f, o_acc = 0.f;
+        // Both products give a warp whole rows (a lane holds four of the 128 dims) and keep eight rows per warp in flight: a
+        // tile of up to 128 positions is ONE round of loads for the scores and one for P V (the rows come from L2 or HBM, so
+        // rounds, not bytes, are what a short context costs).
+        float m_run = -INFINITY, l_run = 0.f;
+        float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int t0 = c0; t0 < c1; t0 += DS_ATTN_TILE) {
             const int n = min(DS_ATTN_TILE, c1 - t0);
             if (t0 > c0) { ds_tile_offsets(p, sh, layer, table, kvh, t0, n, tid_c); ds_sync(); }
-            for (int j0 = cw; j0 < n; j0 += DS_WARPS * 4) {               // four independent rows per warp in flight
-                float4 kr[4];
+            for (int j0 = cw; j0 < n; j0 += DS_WARPS * 8) {
+                float4 kr[8];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
+                for (int i = 0; i < 8; i++) {
                     const int j = j0 + i * DS_WARPS;
                     kr[i] = (j < n) ? __ldg(reinterpret_cast<const float4*>(pool + sh.koff[j]) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
+                for (int i = 0; i < 8; i++) {
                     const int j = j0 + i * DS_WARPS;
                     const float dot = warp_sum(kr[i].x * q4.x + kr[i].y * q4.y + kr[i].z * q4.z + kr[i].w * q4.w);
                     if (lane == 0 && j < n) sh.sc[j] = dot * p.scale;
@@ -414,12 +419,21 @@ __device__ __forceinline__ void ds_attention(const DsParams& p, int layer, int p
             ds_sync();                                               // every warp has read the raw scores
             if (tid_c < n) sh.sc[tid_c] = exp2f((sh.sc[tid_c] - m_new) * LOG2E);
             ds_sync();
-            o_acc *= corr; l_run *= corr; m_run = m_new;
-#pragma unroll 8
-            for (int j = part; j < n; j += DS_ATTN_PARTS) {
-                const float pj = sh.sc[j];
-                o_acc = fmaf(pj, __ldg(pool + sh.koff[j] + vdelta + c), o_acc);
-                l_run += pj;
+            o4.x *= corr; o4.y *= corr; o4.z *= corr; o4.w *= corr; l_run *= corr; m_run = m_new;
+            for (int j0 = cw; j0 < n; j0 += DS_WARPS * 8) {
+                float4 vr[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int j = j0 + i * DS_WARPS;
+                    vr[i] = (j < n) ? __ldg(reinterpret_cast<const float4*>(pool + sh.koff[j] + vdelta) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int j = j0 + i * DS_WARPS;
+                    const float pj = (j < n) ? sh.sc[j] : 0.f;
+                    o4.x = fmaf(pj, vr[i].x, o4.x); o4.y = fmaf(pj, vr[i].y, o4.y); o4.z = fmaf(pj, vr[i].z, o4.z); o4.w = fmaf(pj, vr[i].w, o4.w);
+                    l_run += pj;
+                }
             }
             ds_sync();                                               // sc / koff are rewritten by the next tile
         }
@@ -429,16 +443,23 @@ __device__ __forceinline__ void ds_attention(const DsParams& p, int layer, int p
             const float m_new = fmaxf(m_run, s);
             const float corr = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * LOG2E);
             const float pj = exp2f((s - m_new) * LOG2E);
-            o_acc *= corr; l_run *= corr; m_run = m_new;
-            if (part == 0) { o_acc = fmaf(pj, sh.vnew[c], o_acc); l_run += pj; }
+            o4.x *= corr; o4.y *= corr; o4.z *= corr; o4.w *= corr; l_run *= corr; m_run = m_new;
+            if (cw == 0) {
+                const float4 v4 = *reinterpret_cast<const float4*>(&sh.vnew[lane * 4]);
+                o4.x = fmaf(pj, v4.x, o4.x); o4.y = fmaf(pj, v4.y, o4.y); o4.z = fmaf(pj, v4.z, o4.z); o4.w = fmaf(pj, v4.w, o4.w);
+                l_run += pj;
+            }
         }
-        sh.o_part[part][c] = o_acc;
-        if (c == 0) sh.l_part[part] = l_run;
+        // every warp's share of P V, [warp][128]: in the 8 KB of `partial`, which only the unit loops of the weight phases use
+        // (a CTA-wide barrier lies between them and this point, and another between here and the next weight phase)
+        float (*o_part)[128] = reinterpret_cast<float (*)[128]>(&sh.partial[0][0]);
+        *reinterpret_cast<float4*>(&o_part[cw][lane * 4]) = o4;
+        if (lane == 0) sh.l_part[cw] = l_run;
         ds_sync();
         if (part == 0) {
             float o = 0.f, l = 0.f;
 #pragma unroll
-            for (int i = 0; i < DS_ATTN_PARTS; i++) { o += sh.o_part[i][c]; l += sh.l_part[i]; }
+            for (int i = 0; i < DS_WARPS; i++) { o += o_part[i][c]; l += sh.l_part[i]; }
             if (p.nsplit == 1) ds_st_tagged(p.attn + (size_t)h * 128 + c, o * (l > 0.f ? 1.f / l : 0.f), tag_out);
             else {
                 unsigned long long* dst = p.attn_part + ((size_t)h * p.nsplit + split) * 130;

@@ -16,7 +16,7 @@
 #define DS_STAGES DS_WARPS                          // one ring stage per warp
 #define DS_MAX_PHASES 448                           // 5 per layer + the head: up to 89 layers
 #define DS_ATTN_TILE 256
-#define DS_ATTN_PARTS (DS_THREADS / 128)   // partitions of a tile's positions in the P V product
+
 #define DS_PARTIAL_SLOTS 128                        // per-unit row sums in flight (power of two; > ring stages + 2 * warps + slices per group)
 #define DS_RESIDUAL_ROWS 512                        // residual rows a CTA keeps in shared memory per phase
 #define DS_MAX_SLICES 64                            // K / 512 of the widest matrix
