@@ -410,6 +410,14 @@ __device__ __forceinline__ void ds_attention(const DsParams& p, int layer, int p
                     if (lane == 0 && j < n) sh.sc[j] = dot * p.scale;
                 }
             }
+            // the V rows of this warp's first eight positions do not depend on the scores: requested now, they arrive while the
+            // softmax goes through its three barriers
+            float4 vr[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int j = cw + i * DS_WARPS;
+                vr[i] = (j < n) ? __ldg(reinterpret_cast<const float4*>(pool + sh.koff[j] + vdelta) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             ds_sync();
             float mx = -INFINITY;
             for (int j = lane; j < n; j += 32) mx = fmaxf(mx, sh.sc[j]);
@@ -421,11 +429,12 @@ __device__ __forceinline__ void ds_attention(const DsParams& p, int layer, int p
             ds_sync();
             o4.x *= corr; o4.y *= corr; o4.z *= corr; o4.w *= corr; l_run *= corr; m_run = m_new;
             for (int j0 = cw; j0 < n; j0 += DS_WARPS * 8) {
-                float4 vr[8];
+                if (j0 != cw) {
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int j = j0 + i * DS_WARPS;
-                    vr[i] = (j < n) ? __ldg(reinterpret_cast<const float4*>(pool + sh.koff[j] + vdelta) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int i = 0; i < 8; i++) {
+                        const int j = j0 + i * DS_WARPS;
+                        vr[i] = (j < n) ? __ldg(reinterpret_cast<const float4*>(pool + sh.koff[j] + vdelta) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                 }
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
