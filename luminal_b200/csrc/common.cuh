@@ -210,6 +210,8 @@ int blum_argmax_pairs(blum_ctx* ctx, const float* logits, int64_t rows, int64_t 
 int blum_pick_pairs(blum_ctx* ctx, const int32_t* pairs, int nranks, int64_t rows, int32_t* out_idx);
 
 int blum_gemm_ws_reserve(blum_ctx* ctx, size_t bytes);
+int blum_bf16_small_supported(int64_t N, int64_t K, int ydt, int64_t M);
+int blum_bf16_small_dispatch(blum_ctx* ctx, const void* w, int64_t N, int64_t K, const void* x, void* y, int ydt, int64_t M);
 int blum_tc_gemm(blum_ctx* ctx, int wf, const void* wdata, const void* scales, int64_t w_rows, int N, int K, const void* x,
                  int64_t M, void* y, int ydt, const int* group_offsets, int groups, int rows_per_group_hint, int swiglu = 0);
 

@@ -145,3 +145,21 @@ def test_bf16_dense_matmul(ctx):
     got = ctx.to_host(y, F32, m * n).reshape(m, n)
     assert_parity(got, x.astype(np.float64) @ w.astype(np.float64).T, max_abs=1e-4, rel=1e-4, what="bf16 matmul")
     ctx.check_device_error()
+
+
+@pytest.mark.parametrize("m", [1, 5, 8])
+@pytest.mark.parametrize("n,k", [(5120, 2880), (200, 256), (96, 2880)])
+def test_bf16_dense_matmul_at_decode_row_counts(ctx, m, n, k):
+    """One to eight rows take the streaming kernel (bf16_small.cu): K = 2880 is 22.5 super-blocks of 128 (a ragged last
+    chunk), N = 200 / 96 leave ragged row tasks; f32 and bf16 outputs."""
+    w = round_to_dtype(gen_normal(4, 960 + m, n * k, 0.02).reshape(n, k), BF16)
+    x = round_to_dtype(gen_normal(4, 970 + m, m * k).reshape(m, k), BF16)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    wd, xd = ctx.to_device(w, BF16), ctx.to_device(x, BF16)
+    y = ctx.alloc(m * n * 4)
+    ctx._check(ctx.lib.blum_bf16_matmul(ctx.h, wd.ptr, n, k, xd.ptr, y.ptr, F32, m))
+    assert_parity(ctx.to_host(y, F32, m * n).reshape(m, n), want, max_abs=2e-4 * max(1.0, float(np.abs(want).max())), rel=1e-4, what="bf16 small matmul f32 out")
+    ctx._check(ctx.lib.blum_bf16_matmul(ctx.h, wd.ptr, n, k, xd.ptr, y.ptr, BF16, m))
+    got = ctx.to_host(y, BF16, m * n).reshape(m, n)
+    assert_parity(got, want, max_abs=2.0 ** -8 * float(np.abs(want).max()) + 1e-4, rel=1e-2, what="bf16 small matmul bf16 out")
+    ctx.check_device_error()
