@@ -142,7 +142,6 @@ struct DsShared {
     float l_part[DS_WARPS];                         // every warp's share of the softmax denominator (its share of P V lives in `partial`)
     unsigned long long seq;
     int abort;
-    float resid[DS_RESIDUAL_ROWS];                  // residual rows of the groups this CTA finishes (o_proj / down)
     float pp_sum[16];                               // partial sums of the later CTAs for this CTA's last group
     int pp_state;                                   // phase + 1: pp_sum is valid for that phase
     unsigned long long amax;                        // largest (ordered logit, row) key of this CTA's head rows; 0: none
@@ -170,12 +169,9 @@ __device__ __noinline__ void ds_stage_slice(const DsParams& p, int kind, int lay
     const int kbase = slice * DS_UNIT_K;
     float ss = 0.f;
     // one step of four consecutive elements: norm weight, block maximum over the 8 lanes of a 32-element block, digits
-    auto put = [&](float (&v)[4], int k) {
+    auto put = [&](float (&v)[4], int k, const float4 nw) {      // nw: the norm weights of these four elements (ones without a norm)
         ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-        if (norm_w) {
-            const float4 nw = __ldg(reinterpret_cast<const float4*>(norm_w + k));
-            v[0] *= nw.x; v[1] *= nw.y; v[2] *= nw.z; v[3] *= nw.w;
-        }
+        v[0] *= nw.x; v[1] *= nw.y; v[2] *= nw.z; v[3] *= nw.w;
         float mx = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -202,6 +198,7 @@ __device__ __noinline__ void ds_stage_slice(const DsParams& p, int kind, int lay
         *reinterpret_cast<unsigned*>(blk + 64) = pc;
         if ((k & 31) == 0) xsc[k >> 5] = down;
     };
+    auto norm_at = [&](int k) { return norm_w ? __ldg(reinterpret_cast<const float4*>(norm_w + k)) : make_float4(1.f, 1.f, 1.f, 1.f); };
     constexpr int PASS = 128;                                     // elements a warp covers per pass (4 per lane)
     if (from_embed) {
         // layer 0 reads the embedding row itself
@@ -213,15 +210,19 @@ __device__ __noinline__ void ds_stage_slice(const DsParams& p, int kind, int lay
             const int k = kbase + i * PASS + lane * 4;
             const float4 e = __ldg(reinterpret_cast<const float4*>(erow + k));
             float v[4] = {e.x, e.y, e.z, e.w};
-            put(v, k);
+            put(v, k, norm_at(k));
         }
     } else if (!combine) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
             const int k0 = kbase + half * 2 * PASS + lane * 4;
+            // the norm weights do not depend on the words: requested with them, not after them (one L2 round trip less per half)
+            const float4 nw0 = norm_at(k0), nw1 = norm_at(k0 + PASS);
             ulonglong2 buf[2][2];
             // All words of the round are requested together, and those that still carry an older tag are requested together
-            // again: one round trip per attempt, however many of them are late.
+            // again: one round trip per attempt, however many of them are late.  (All 16 words of a lane in one round, or
+            // the second half requested before the first is digitised, were measured slower, 1.80 -> 1.90 / 1.82 ms per
+            // step: the registers they take are spilled around the call, and one big round doubles the polling traffic.)
             unsigned ready = 0;
             const unsigned long long t0 = blum_globaltimer();
             for (uint32_t spin = 0;; spin++) {
@@ -239,7 +240,7 @@ __device__ __noinline__ void ds_stage_slice(const DsParams& p, int kind, int lay
 #pragma unroll
             for (int i = 0; i < 2; i++) {
                 float v[4] = {ds_val_of(buf[i][0].x), ds_val_of(buf[i][0].y), ds_val_of(buf[i][1].x), ds_val_of(buf[i][1].y)};
-                put(v, k0 + i * PASS);
+                put(v, k0 + i * PASS, i ? nw1 : nw0);
             }
         }
     } else {
@@ -262,7 +263,7 @@ __device__ __noinline__ void ds_stage_slice(const DsParams& p, int kind, int lay
             const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll
             for (int e = 0; e < 4; e++) v[e] *= inv;
-            put(v, k);
+            put(v, k, norm_at(k));
         }
     }
     ss = warp_sum(ss);
@@ -604,15 +605,6 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
         const uint32_t tag = ds_tag(seq, p.nphases, ph);
         long long* tl = (p.prof && P.layer == p.prof_layer && tid_c == 0) ? p.prof + (size_t)ncta * 32 + (size_t)cta * 64 + P.kind * 8 : nullptr;
         if (tl) tl[0] = (long long)blum_globaltimer();
-        // groups whose first slice this CTA holds finish here: [gh0, gh1); for o_proj / down their residual rows (written
-        // by the previous residual add, or the embedding row) are fetched now; the weight phase before this one does not
-        // use the buffer, so warps that are still in it are not disturbed
-        const int gh0 = (u0 + S - 1) / S, gh1 = (u1 + S - 1) / S;
-        if (P.kind == DS_O || P.kind == DS_DOWN) {
-            const uint32_t rtag = ds_tag(seq, p.nphases, P.kind == DS_O ? ph - 3 : ph - 2);
-            const int nres = min((gh1 - gh0) * DS_UNIT_ROWS, DS_RESIDUAL_ROWS);
-            for (int i = tid_c; i < nres; i += DS_THREADS) sh.resid[i] = ds_wait_value(p.xres + (size_t)gh0 * DS_UNIT_ROWS + i, rtag, p, s_abort, 2);
-        }
         ds_sync();                          // the previous phase's warps are done with x and the reduction scratch
         if (tl) tl[1] = (long long)blum_globaltimer();
         // The ring is full and stays so while x is waited for and staged.  So that HBM does not idle meanwhile, every warp
@@ -790,9 +782,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
                             }
                         }
                         else {                                                              // o_proj / down: residual add in place
-                            const int ri = row - gh0 * DS_UNIT_ROWS;
+                            // the residual row was written two or three phases ago: one L2 read here.  (Fetching a CTA's residual
+                            // rows into shared memory at the start of the phase put a round trip and a barrier in front of
+                            // every o_proj / down phase and was 10 us per step slower.)
                             const uint32_t rtag = ds_tag(seq, p.nphases, P.kind == DS_O ? ph - 3 : ph - 2);
-                            const float base = (ri >= 0 && ri < DS_RESIDUAL_ROWS) ? sh.resid[ri] : ds_wait_value(p.xres + row, rtag, p, s_abort, 2);
+                            const float base = ds_wait_value(p.xres + row, rtag, p, s_abort, 2);
                             ds_st_tagged(p.xres + row, base + v, tag);
                         }
                     }

@@ -18,7 +18,6 @@
 #define DS_ATTN_TILE 256
 
 #define DS_PARTIAL_SLOTS 128                        // per-unit row sums in flight (power of two; > ring stages + 2 * warps + slices per group)
-#define DS_RESIDUAL_ROWS 512                        // residual rows a CTA keeps in shared memory per phase
 #define DS_MAX_SLICES 64                            // K / 512 of the widest matrix
 #define DS_PREFETCH_UNITS 2                         // units per warp pulled into L2 at the start of a phase
 
