@@ -520,6 +520,9 @@ __device__ __forceinline__ bool ds_fetch_partners(const DsParams& p, int units, 
     return true;
 }
 
+// PROF: the development counters and timestamps (blum_llama_stream_profile); the product launches the kernel without them:
+// they cost clock reads per unit and registers the unit loop has no room for
+template <bool PROF>
 __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __grid_constant__ DsParams p) {
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ __align__(16) DsShared sh;
@@ -587,23 +590,24 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
         for (int k = tid_c; k < p.H; k += DS_THREADS) ds_st_tagged(p.xres + k, __ldg(p.embed + (size_t)id * p.H + k), tag0);
     }
     int nbase = 0;                        // units of this CTA consumed in earlier phases
-    const long long ct0 = clock64();
+    auto now = [&]() -> long long { if constexpr (PROF) return clock64(); else return 0; };
+    const long long ct0 = now();
     long long c_full = 0, c_stage = 0, c_attn = 0, c_seg = 0;
     long long k_stage[6] = {0, 0, 0, 0, 0, 0}, k_loop[6] = {0, 0, 0, 0, 0, 0};
     for (int ph = 0; ph < p.nphases; ph++) {
         const DsPhase P = phases[ph];
         if (P.kind == DS_ATTN) {
-            const long long a0 = clock64();
+            const long long a0 = now();
             ds_attention(p, P.layer, ph, seq, sh, tid_c, cta, ncta, s_abort);
-            c_attn += clock64() - a0;
-            k_loop[DS_ATTN] += clock64() - a0;
+            c_attn += now() - a0;
+            if constexpr (PROF) k_loop[DS_ATTN] += now() - a0;
             continue;
         }
         const int S = P.S, units = P.groups * S;
         const int u0 = sh.range[ph].x, u1 = sh.range[ph].y;
         if (u1 <= u0) continue;                   // nothing of this matrix here: its x is not needed either
         const uint32_t tag = ds_tag(seq, p.nphases, ph);
-        long long* tl = (p.prof && P.layer == p.prof_layer && tid_c == 0) ? p.prof + (size_t)ncta * 32 + (size_t)cta * 64 + P.kind * 8 : nullptr;
+        long long* tl = (PROF && p.prof && P.layer == p.prof_layer && tid_c == 0) ? p.prof + (size_t)ncta * 32 + (size_t)cta * 64 + P.kind * 8 : nullptr;
         if (tl) tl[0] = (long long)blum_globaltimer();
         ds_sync();                          // the previous phase's warps are done with x and the reduction scratch
         if (tl) tl[1] = (long long)blum_globaltimer();
@@ -625,7 +629,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
             const DsPhase N = phases[ph + 1 + (phases[ph + 1].kind == DS_ATTN ? 1 : 0)];
             if (N.norm_w) for (int k = tid_c * 32; k < N.K; k += DS_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(N.norm_w + k));
         }
-        const long long l0 = clock64();
+        const long long l0 = now();
         // the last group of the range continues in later CTAs if the range ends inside it
         const bool split_tail = (u1 % S != 0) && ((u1 / S) * S >= u0);
         const int first = (cw - nbase % NS + NS) % NS;
@@ -646,14 +650,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
                 }
             }
             {
-                const long long e0 = clock64();
+                const long long e0 = now();
                 ds_ensure_slice(p, P, ph, seq, sh, xpl, xsc, lane, s, s_abort);
-                if (cw == 0) { c_stage += clock64() - e0; k_stage[P.kind] += clock64() - e0; }
+                if constexpr (PROF) { if (cw == 0) { c_stage += now() - e0; k_stage[P.kind] += now() - e0; } }
                 if (tl && u == u0 + first) tl[3] = (long long)blum_globaltimer();
             }
-            const long long f0 = clock64();
+            const long long f0 = now();
             ds_mbar_wait(&sh.full[cw], par, p, s_abort, 1, n);
-            c_full += clock64() - f0;
+            c_full += now() - f0;
             const unsigned char* st = ring + (size_t)cw * DS_UNIT_BYTES;
             // block scales of this lane's two rows and the scales of x for the slice's 16 blocks
             uint32_t dlo[8], dhi[8];
@@ -689,7 +693,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
             if (lane == 0) { outstanding = false; request(); ds_cursor_advance(phases, p.nphases, sh, rf, NS); rf_n += NS; }
 
             // ---- the unit's 16 row sums: lane t=0 of a row pair holds planes 0 and 1 (columns 0, 1), lane t=1 plane 2
-            const long long g0c = clock64();
+            const long long g0c = now();
             const float p2_lo = __shfl_down_sync(0xffffffffu, acc0, 1), p2_hi = __shfl_down_sync(0xffffffffu, acc2, 1);
             const int pslot = n & (DS_PARTIAL_SLOTS - 1);
             // The warps are not coupled to each other: one whose units keep hitting L2 can run many units ahead of one whose
@@ -792,10 +796,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
                     }
                 }
             }
-            c_seg += clock64() - g0c;
+            c_seg += now() - g0c;
         }
         nbase += u1 - u0;
-        k_loop[P.kind] += clock64() - l0;
+        if constexpr (PROF) k_loop[P.kind] += now() - l0;
         if (tl) tl[4] = (long long)blum_globaltimer();
     }
     // a copy this warp requested and never consumed (only after an abort) has to land before the CTA's shared memory goes away
@@ -803,10 +807,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const __gr
         const unsigned long long t0 = blum_globaltimer();
         while (!ds_mbar_try(&sh.full[cw], (uint32_t)((req_n / NS) & 1)) && blum_globaltimer() - t0 < DS_TIMEOUT_NS) {}
     }
-    if (p.prof && tid_c == 0) {
+    if (PROF && p.prof && tid_c == 0) {
         long long* o = p.prof + cta * 32;
         for (int k = 0; k < 6; k++) { o[8 + 3 * k] = k_stage[k]; o[9 + 3 * k] = k_loop[k]; o[10 + 3 * k] = 0; }
-        o[0] = clock64() - ct0; o[1] = c_full; o[2] = 0; o[3] = c_stage; o[4] = c_attn; o[5] = c_seg; o[6] = 0; o[7] = 0;
+        o[0] = now() - ct0; o[1] = c_full; o[2] = 0; o[3] = c_stage; o[4] = c_attn; o[5] = c_seg; o[6] = 0; o[7] = 0;
     }
     if (p.pick) {
         // ---- next token inside the kernel: every CTA publishes its best (key, row); CTA 0 takes the maximum, and only when
@@ -904,11 +908,13 @@ int blum_ds_launch(blum_ctx* ctx, const DsParams& p) {
     static bool attr_set[64] = {};
     const size_t smem = blum_ds_smem_bytes(p.kmax);
     if (ctx->device >= 0 && ctx->device < 64 && !attr_set[ctx->device]) {
-        BLUM_CUDA(ctx, cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - 24 * 1024)));
+        BLUM_CUDA(ctx, cudaFuncSetAttribute(decode_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - 24 * 1024)));
+        BLUM_CUDA(ctx, cudaFuncSetAttribute(decode_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ctx->smem_optin - 24 * 1024)));
         attr_set[ctx->device] = true;
     }
     void* args[] = {(void*)&p};
-    BLUM_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)decode_stream_kernel, dim3(ctx->sm_count), dim3(DS_THREADS), args, smem, ctx->stream));
+    const void* kern = p.prof ? (const void*)decode_stream_kernel<true> : (const void*)decode_stream_kernel<false>;
+    BLUM_CUDA(ctx, cudaLaunchCooperativeKernel(kern, dim3(ctx->sm_count), dim3(DS_THREADS), args, smem, ctx->stream));
     ctx->launches++;
     return BLUM_OK;
 }
