@@ -213,35 +213,50 @@ __device__ __noinline__ void ds_stage_slice(const DsParams& p, int kind, int lay
             put(v, k, norm_at(k));
         }
     } else if (!combine) {
+        // Two halves of 8 words per lane.  The norm weights do not depend on the words and are requested with them; the second
+        // half's first request goes out before the first half is digitised, so that its round trip overlaps that work.  Words
+        // that still carry an older tag are requested together again: one round trip per attempt, however many are late.
+        // (All 16 words of a lane polled as one round was measured slower: twice the polling traffic while producers are late.)
+        const int kA = kbase + lane * 4, kB = kA + 2 * PASS;
+        ulonglong2 bufA[2][2], bufB[2][2];
+        auto request = [&](ulonglong2 (&buf)[2][2], int k0, unsigned ready) {
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int k0 = kbase + half * 2 * PASS + lane * 4;
-            // the norm weights do not depend on the words: requested with them, not after them (one L2 round trip less per half)
-            const float4 nw0 = norm_at(k0), nw1 = norm_at(k0 + PASS);
-            ulonglong2 buf[2][2];
-            // All words of the round are requested together, and those that still carry an older tag are requested together
-            // again: one round trip per attempt, however many of them are late.  (All 16 words of a lane in one round, or
-            // the second half requested before the first is digitised, were measured slower, 1.80 -> 1.90 / 1.82 ms per
-            // step: the registers they take are spilled around the call, and one big round doubles the polling traffic.)
+            for (int i = 0; i < 2; i++)
+                if (!((ready >> i) & 1u)) { buf[i][0] = ds_ld_word2(src + k0 + i * PASS); buf[i][1] = ds_ld_word2(src + k0 + i * PASS + 2); }
+        };
+        auto arrived = [&](const ulonglong2 (&buf)[2][2], unsigned ready) {
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+                if (ds_tag_of(buf[i][0].x) == tag && ds_tag_of(buf[i][0].y) == tag && ds_tag_of(buf[i][1].x) == tag && ds_tag_of(buf[i][1].y) == tag)
+                    ready |= 1u << i;
+            return ready;
+        };
+        auto wait_all = [&](ulonglong2 (&buf)[2][2], int k0) {       // first request already issued
             unsigned ready = 0;
             const unsigned long long t0 = blum_globaltimer();
             for (uint32_t spin = 0;; spin++) {
-#pragma unroll
-                for (int i = 0; i < 2; i++)
-                    if (!((ready >> i) & 1u)) { buf[i][0] = ds_ld_word2(src + k0 + i * PASS); buf[i][1] = ds_ld_word2(src + k0 + i * PASS + 2); }
-#pragma unroll
-                for (int i = 0; i < 2; i++)
-                    if (ds_tag_of(buf[i][0].x) == tag && ds_tag_of(buf[i][0].y) == tag && ds_tag_of(buf[i][1].x) == tag && ds_tag_of(buf[i][1].y) == tag)
-                        ready |= 1u << i;
+                ready = arrived(buf, ready);
                 if (__all_sync(0xffffffffu, ready == 3u || *s_abort)) break;
                 if (lane == 0 && (spin & 15u) == 15u && !ds_aborted(p, s_abort) && blum_globaltimer() - t0 > DS_TIMEOUT_NS)
                     ds_give_up(p.err, p.ctr, s_abort, 2, (long long)tag, (long long)k0);
+                request(buf, k0, ready);
             }
+        };
+        const float4 nwA0 = norm_at(kA), nwA1 = norm_at(kA + PASS);
+        request(bufA, kA, 0u);
+        wait_all(bufA, kA);
+        const float4 nwB0 = norm_at(kB), nwB1 = norm_at(kB + PASS);
+        request(bufB, kB, 0u);
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
-                float v[4] = {ds_val_of(buf[i][0].x), ds_val_of(buf[i][0].y), ds_val_of(buf[i][1].x), ds_val_of(buf[i][1].y)};
-                put(v, k0 + i * PASS, i ? nw1 : nw0);
-            }
+        for (int i = 0; i < 2; i++) {
+            float v[4] = {ds_val_of(bufA[i][0].x), ds_val_of(bufA[i][0].y), ds_val_of(bufA[i][1].x), ds_val_of(bufA[i][1].y)};
+            put(v, kA + i * PASS, i ? nwA1 : nwA0);
+        }
+        wait_all(bufB, kB);
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            float v[4] = {ds_val_of(bufB[i][0].x), ds_val_of(bufB[i][0].y), ds_val_of(bufB[i][1].x), ds_val_of(bufB[i][1].y)};
+            put(v, kB + i * PASS, i ? nwB1 : nwB0);
         }
     } else {
         for (int i = 0; i < DS_UNIT_K / PASS; i++) {
