@@ -26,7 +26,7 @@ CFG = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=143
 PROMPT_LEN = 32
 SEED = 0
 # DRAM bytes / algorithmic bytes of decode_stream_kernel, from the ncu capture summarised in profiles/decode_stream_8b_4layers.md
-NCU_TRAFFIC_RATIO = 1.007    # DRAM bytes / algorithmic bytes of decode_stream_kernel (profiles/decode_stream_8b_4layers.md)
+NCU_TRAFFIC_RATIO = 1.003    # DRAM bytes / algorithmic bytes of decode_stream_kernel (profiles/decode_stream_8b_4layers.md)
 
 
 def measured_peaks():
