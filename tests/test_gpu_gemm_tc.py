@@ -65,6 +65,11 @@ def test_operator_sweep_sizes_on_a_sub_block(ctx, k, n):
         tol = max(1e-2, 2.0 ** -8 * np.abs(want).max() + 5e-3)       # as in check(): one bf16 rounding step of the output
         assert_parity(got, want, max_abs=tol, what="tc gemm sub-block N=%d K=%d M=%d" % (n, k, m))
         assert np.abs(got - want).mean() < 4e-3 * np.abs(want).mean()
+        if m == 700:
+            # the same ragged product with f32 output (two token tiles per CTA, f32 stores): no output rounding
+            got32 = ctx.to_host(QuantizedMatmul(ctx, BF16, F32).process(ctx.to_device(x, BF16), w, m), F32, m * n).reshape(m, n)[np.ix_(rows, cols)]
+            ctx.check_device_error()
+            assert_parity(got32, want, max_abs=1e-2, what="tc gemm sub-block f32 out N=%d K=%d M=%d" % (n, k, m))
     w.free()
 
 
